@@ -57,7 +57,15 @@ struct Params {
                                          // (cap_log2 = 0: none)
     int* status;                         // device status word (a bounded wait that ran out)
     long long n_pages;                   // pages of the pool: [Hkv, pages, block, HD]
+    const float* sink;                   // [H] or nullptr: exp(sink_h) joins the softmax's
+                                         // denominator, a term without key or value
 };
+
+// What a sink adds to a row's sum of exponentials taken relative to the maximum m (log2
+// domain): 2^(sink * log2(e) - m).  A row without keys (m = -inf) has no output anyway.
+__device__ __forceinline__ float sink_term(const Params& P, int head, float m) {
+    return (P.sink && m != -INFINITY) ? exp2f(P.sink[head] * LOG2E - m) : 0.f;
+}
 
 // A raw score q . k in the log2 domain of the softmax: times scale * log2(e), or, with a cap
 // c on the scores, c * tanh(raw * scale / c) * log2(e) with tanh(x) = 1 - 2 / (1 + e^(2x)).
@@ -335,6 +343,10 @@ __global__ void __launch_bounds__(NT) attention_tile_kernel(const Params P) {
     lA += __shfl_xor_sync(0xffffffffu, lA, 2);
     lB += __shfl_xor_sync(0xffffffffu, lB, 1);
     lB += __shfl_xor_sync(0xffffffffu, lB, 2);
+    if (P.sink) {
+        if (rA < rows) lA += sink_term(P, kvh * P.group + rA % P.group, mA);
+        if (rB < rows) lB += sink_term(P, kvh * P.group + rB % P.group, mB);
+    }
     const float invA = lA > 0.f ? 1.f / lA : 0.f, invB = lB > 0.f ? 1.f / lB : 0.f;
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
@@ -530,8 +542,10 @@ __global__ void __launch_bounds__(NT) attention_split_kernel(const Params P) {
                 acc += o_s[((size_t)w * 16 + row) * HD + d] * c;
             }
         }
-        const float val = l > 0.f ? acc / l : 0.f;
         const int i = row / P.group, g = row - i * P.group;
+        // one stretch: the sink joins here; several: where the stretches are merged
+        if (P.n_split == 1) l += sink_term(P, kvh * P.group + g, m);
+        const float val = l > 0.f ? acc / l : 0.f;
         const size_t unit = (size_t)(tok0 + i) * P.n_heads + (kvh * P.group + g);
         if (P.n_split == 1) {
             P.out[unit * HD + d] = __float2bfloat16_rn(val);
@@ -593,7 +607,7 @@ __global__ void attention_merge_kernel(const Params P) {
             wsum += w;
         }
         wsum = warp_sum(wsum);
-        if (threadIdx.x == 0) total = wsum;
+        if (threadIdx.x == 0) total = wsum + sink_term(P, h, m);
     }
     __syncthreads();
     const float wsum = total;
@@ -1061,8 +1075,10 @@ attention_split_tma_kernel(const Params P, const Fused F,
                 acc += o_s[((size_t)w * 16 + row) * HD + d] * c;
             }
         }
-        const float val = l > 0.f ? acc / l : 0.f;
         const int i = row / P.group, g = row - i * P.group;
+        // one stretch: the sink joins here; several: where the stretches are merged
+        if (P.n_split == 1) l += sink_term(P, kvh * P.group + g, m);
+        const float val = l > 0.f ? acc / l : 0.f;
         const size_t unit = (size_t)(tok0 + i) * P.n_heads + (kvh * P.group + g);
         if (P.n_split == 1) {
             P.out[unit * HD + d] = __float2bfloat16_rn(val);
@@ -1112,6 +1128,7 @@ attention_split_tma_kernel(const Params P, const Fused F,
                 }
             }
             const int i = row / P.group, g = row - i * P.group;
+            wsum += sink_term(P, kvh * P.group + g, m);
             const size_t unit = (size_t)(tok0 + i) * P.n_heads + (kvh * P.group + g);
             P.out[unit * HD + d] = __float2bfloat16_rn(wsum > 0.f ? acc / wsum : 0.f);
         }
@@ -1325,6 +1342,10 @@ attention_tile_tma_kernel(const Params P, const __grid_constant__ CUtensorMap km
     lA += __shfl_xor_sync(0xffffffffu, lA, 2);
     lB += __shfl_xor_sync(0xffffffffu, lB, 1);
     lB += __shfl_xor_sync(0xffffffffu, lB, 2);
+    if (P.sink) {
+        if (rA < rows) lA += sink_term(P, kvh * P.group + rA % P.group, mA);
+        if (rB < rows) lB += sink_term(P, kvh * P.group + rB % P.group, mB);
+    }
     const float invA = lA > 0.f ? 1.f / lA : 0.f, invB = lB > 0.f ? 1.f / lB : 0.f;
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
@@ -1412,7 +1433,8 @@ constexpr int SPLIT_SMEM_MERGE = (128 + 4 * 16 * HD) * 4;
 constexpr int SPLIT_SMEM = SPLIT_SMEM_PIPE > SPLIT_SMEM_MERGE ? SPLIT_SMEM_PIPE : SPLIT_SMEM_MERGE;
 }  // namespace
 
-// softcap c > 0: scores become c * tanh(score / c) before the softmax.
+// softcap c > 0: scores become c * tanh(score / c) before the softmax.  sink (float32 [H] or
+// nullptr): exp(sink_h) joins the denominator of head h's softmax.
 // n_tiles: 64-row tiles the tile kernel has to run (0: none); n_small: 1 if any
 // request goes to the split kernel.  part_o / part_lse are scratch memory of
 // n_split * T * H * (HD + 1) floats, needed when n_split > 1.
@@ -1422,7 +1444,7 @@ MLS_API int mls_attention_mma(const void* qkv, void* out, const void* k_pool, co
                               int block_size, float scale, int window, float softcap, int n_tiles,
                               int n_small, int n_split, float* part_o, float* part_lse,
                               long long pool_pages, int* status, int use_tma,
-                              cudaStream_t stream) {
+                              const float* sink, cudaStream_t stream) {
     if (n_tokens <= 0 || n_req <= 0) return 0;
     if (n_heads % n_kv || n_split < 1 || n_split > MAX_SPLITS ||
         (n_split > 1 && (!part_o || !part_lse)))
@@ -1463,6 +1485,7 @@ MLS_API int mls_attention_mma(const void* qkv, void* out, const void* k_pool, co
     P.tanh_arg = softcap > 0.f ? 2.0f * LOG2E * scale / softcap : 0.f;
     P.status = status;
     P.n_pages = pool_pages;
+    P.sink = sink;
     const bool tma_ok = use_tma && (block_size == 8 || block_size == 16 || block_size == 32 ||
                                     block_size == 64) && (HD % 64 == 0);
     (void)tma_ok;
@@ -1581,6 +1604,7 @@ MLS_API int mls_attention_decode_fused(const float* parts, int n_parts, long lon
     P.tanh_arg = softcap > 0.f ? 2.0f * LOG2E * scale / softcap : 0.f;
     P.status = status;
     P.n_pages = pool_pages;
+    P.sink = nullptr;                    // the fused step serves mixers without sinks
     Fused F;
     F.parts = parts;
     F.n_parts = n_parts;

@@ -7,7 +7,8 @@
 // aligned causal mask with p = i + Sk - Sq); P = softmax(S); O = P . V in
 // float32, rounded once.  q head h reads kv head h / G.  With a window w, keys
 // j <= p - w are hidden too.  With a cap c > 0 the score becomes c * tanh(S / c) before
-// the softmax.  The paged walk follows the reference's decode
+// the softmax.  With sinks (one learned number per q head) the softmax's denominator also
+// holds exp(sink_h): a term without key or value, not scaled and not capped.  The paged walk follows the reference's decode
 // kernel (kernels/paged_attention.py:34-88): page = table[r, j / block],
 // offset = j % block, online softmax over chunks of keys.
 //
@@ -63,7 +64,8 @@ attention_simt_kernel(const T* __restrict__ qkv, T* __restrict__ out,
                       const int* __restrict__ block_table, int max_blocks,
                       const int* __restrict__ positions, const int* __restrict__ req_of_token,
                       int n_tokens, int n_heads, int n_kv, int hd, int block_size, float scale,
-                      int window, float softcap, long long n_pages) {
+                      int window, float softcap, long long n_pages,
+                      const float* __restrict__ sink) {
     chain_release();
     chain_wait();
     __shared__ float q_s[WARPS][MAX_HD];
@@ -120,6 +122,7 @@ attention_simt_kernel(const T* __restrict__ qkv, T* __restrict__ out,
         m = m_new;
     }
     T* op = out + (size_t)t * n_heads * hd + (size_t)h * hd;
+    if (sink) l += expf(sink[h] - m);         // every token sees itself: m is a number
     const float inv = 1.0f / l;
 #pragma unroll
     for (int i = 0; i < MAX_HD / 32; ++i) {
@@ -133,7 +136,8 @@ MLS_API int mls_attention_simt(const void* qkv, void* out, int dtype, const void
                                const void* v_pool, const int* block_table, int max_blocks,
                                const int* positions, const int* req_of_token, int n_tokens,
                                int n_heads, int n_kv, int hd, int block_size, float scale,
-                               int window, float softcap, long long n_pages, cudaStream_t stream) {
+                               int window, float softcap, long long n_pages, const float* sink,
+                               cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hd > MAX_HD || hd <= 0 || n_heads % n_kv) return MLS_ERR_UNSUPPORTED;
     const long long units = (long long)n_tokens * n_heads;
@@ -143,11 +147,11 @@ MLS_API int mls_attention_simt(const void* qkv, void* out, int dtype, const void
                    stream, (const __nv_bfloat16*)qkv, (__nv_bfloat16*)out,
                    (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, block_table,
                    max_blocks, positions, req_of_token, n_tokens, n_heads, n_kv, hd, block_size,
-                   scale, window, softcap, n_pages);
+                   scale, window, softcap, n_pages, sink);
     else
         MLS_LAUNCH((attention_simt_kernel<float>), dim3(blocks), dim3(WARPS * 32), 0, stream,
                    (const float*)qkv, (float*)out, (const float*)k_pool, (const float*)v_pool,
                    block_table, max_blocks, positions, req_of_token, n_tokens, n_heads, n_kv, hd,
-                   block_size, scale, window, softcap, n_pages);
+                   block_size, scale, window, softcap, n_pages, sink);
     return launch_status();
 }

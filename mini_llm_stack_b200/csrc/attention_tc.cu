@@ -77,6 +77,8 @@ struct Params {
                                          // (cap_over_scale = 0: none)
     int* status;
     long long n_pages;                   // pages of the pool: [Hkv, pages, block, HD]
+    const float* sink;                   // [H] or nullptr: exp(sink_h) joins the softmax's
+                                         // denominator, a term without key or value
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -450,7 +452,9 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
             timed_out = true;
         tc_fence_after();
         if (P.two_tiles) {
-            // the chain's rows are its own: O / l
+            // the chain's rows are its own: O / l (the sink's term relative to the maximum in use)
+            if (P.sink && live && m_used != -INFINITY)
+                l += exp2f(P.sink[kvh * P.group + g] * LOG2E - m_used);
             const float inv = l > 0.f ? 1.0f / l : 0.f;
             __nv_bfloat16* dst = P.out + (size_t)(tok0 + ti) * P.n_heads * HD +
                                  (size_t)(kvh * P.group + g) * HD;
@@ -487,7 +491,8 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
             const float m = fmaxf(s0.x, s1.x);
             const float f0 = s0.x == -INFINITY ? 0.f : fast_exp2(s0.x - m);
             const float f1 = s1.x == -INFINITY ? 0.f : fast_exp2(s1.x - m);
-            const float l_row = s0.y * f0 + s1.y * f1;
+            float l_row = s0.y * f0 + s1.y * f1;
+            if (P.sink && live && m != -INFINITY) l_row += exp2f(P.sink[kvh * P.group + g] * LOG2E - m);
             const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
             const float w0 = f0 * inv, w1 = f1 * inv;
             const bool second = n_steps[1] > 0;            // else its accumulator was never written
@@ -584,7 +589,7 @@ MLS_API int mls_attention_tc(const void* qkv, void* out, const void* k_pool, con
                              const int* ctx_len, int n_req, int n_heads, int n_kv, int block_size,
                              float scale, int window, float softcap, int n_tiles, int n_tiles_wide,
                              int skip_small, long long pool_pages, int* status,
-                             cudaStream_t stream) {
+                             const float* sink, cudaStream_t stream) {
 #if MLS_HEAD_DIM == 64 || MLS_HEAD_DIM == 128
     if (n_tiles <= 0 || n_req <= 0) return 0;
     if (n_heads % n_kv) return MLS_ERR_UNSUPPORTED;
@@ -624,6 +629,7 @@ MLS_API int mls_attention_tc(const void* qkv, void* out, const void* k_pool, con
     P.tanh_arg = softcap > 0.f ? 2.0f * LOG2E * scale / softcap : 0.f;
     P.status = status;
     P.n_pages = pool_pages;
+    P.sink = sink;
     MLS_LAUNCH((attention_tc_kernel), dim3(n_kv, P.two_tiles ? n_tiles_wide : n_tiles),
                dim3(THREADS), SMEM_BYTES, stream, P, kmap, vmap, kmap_wide, vmap_wide);
     return launch_status();

@@ -1,9 +1,11 @@
 // Routed experts: choose, sort, multiply expert by expert, add up.
 //
-// mls_route_topk: scores s = sigmoid(z) of float32 router logits z [T, E]; for every
-//   token the `top` largest scores (the lowest index wins a tie) with the scores
-//   themselves as weights (optionally renormalised to sum 1).  A (token, choice) pair is
-//   a "slot": slot = t * top + j.
+// mls_route_topk: scores s = sigmoid(z), or softmax(z) over all outputs, of float32 router
+//   logits z [T, E]; for every token the `top` largest scores (plus a per-output correction
+//   that enters the choice only; the lowest index wins a tie) with the scores themselves as
+//   weights (optionally divided by their sum + renorm_eps).  A (token, choice) pair is a
+//   "slot": slot = t * top + j.  Outputs n_real .. E-1 stand for experts without weights that
+//   return their input: they get no tiles, and mls_expert_combine adds weight * h for them.
 // mls_route_sort: slots ordered by expert: order[p] = slot, offsets[E + 1], and the list
 //   of row tiles (tile_expert, tile_row0) the products below walk.  One CTA.
 // mls_expert_glu: y[p, :] = silu(Wg[e] a) * (Wu[e] a) with a = weight[slot] * h[token]
@@ -24,8 +26,9 @@ namespace {
 constexpr int BM = 32, BN = 64, BK = 32, TM = 2, TN = 4;   // 256 threads
 
 __global__ void route_topk_kernel(const float* __restrict__ logits, int n_tokens, int n_experts,
-                                  int top, int renorm, int* __restrict__ idx,
-                                  float* __restrict__ weight) {
+                                  int top, int renorm, int softmax,
+                                  const float* __restrict__ correction, float renorm_eps,
+                                  int* __restrict__ idx, float* __restrict__ weight) {
     chain_release();
     chain_wait();
     // one warp a token
@@ -33,45 +36,60 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, int n_tokens
     const int t = blockIdx.x * (blockDim.x >> 5) + warp;
     if (t >= n_tokens) return;
     const float* z = logits + (size_t)t * n_experts;
+    // softmax over all outputs: the largest logit and the sum of exponentials, both in the
+    // order of the lanes' strides, so a token's scores do not depend on its batch
+    float z_max = 0.f, inv_sum = 1.f;
+    if (softmax) {
+        z_max = -INFINITY;
+        for (int e = lane; e < n_experts; e += 32) z_max = fmaxf(z_max, z[e]);
+        z_max = warp_max(z_max);
+        float sum = 0.f;
+        for (int e = lane; e < n_experts; e += 32) sum += expf(z[e] - z_max);
+        inv_sum = 1.0f / warp_sum(sum);
+    }
     float total = 0.f;
     for (int j = 0; j < top; ++j) {
-        float best = -1.f;
+        float best = -INFINITY, best_s = 0.f;
         int arg = 0x7fffffff;
         for (int e = lane; e < n_experts; e += 32) {
             bool taken = false;
             for (int p = 0; p < j; ++p) taken |= idx[(size_t)t * top + p] == e;
-            const float s = 1.0f / (1.0f + expf(-z[e]));
-            if (!taken && (s > best || (s == best && e < arg))) {
-                best = s;
+            const float s = softmax ? expf(z[e] - z_max) * inv_sum : 1.0f / (1.0f + expf(-z[e]));
+            const float c = correction ? s + correction[e] : s;      // the choice's score
+            if (!taken && (c > best || (c == best && e < arg))) {
+                best = c;
+                best_s = s;
                 arg = e;
             }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const float os = __shfl_xor_sync(0xffffffffu, best_s, o);
             const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
             if (ob > best || (ob == best && oa < arg)) {
                 best = ob;
+                best_s = os;
                 arg = oa;
             }
         }
         if (arg >= n_experts) {                  // only scores that are not numbers were left
             arg = 0;
-            best = 0.f;
+            best_s = 0.f;
         }
         if (lane == 0) {
             idx[(size_t)t * top + j] = arg;
-            weight[(size_t)t * top + j] = best;
+            weight[(size_t)t * top + j] = best_s;
         }
-        total += best;
+        total += best_s;
         __syncwarp();
     }
     if (renorm && lane == 0)
-        for (int j = 0; j < top; ++j) weight[(size_t)t * top + j] /= total;
+        for (int j = 0; j < top; ++j) weight[(size_t)t * top + j] /= total + renorm_eps;
 }
 
 __global__ void __launch_bounds__(1024)
-route_sort_kernel(const int* __restrict__ idx, int n_slots, int n_experts,
+route_sort_kernel(const int* __restrict__ idx, int n_slots, int n_experts, int n_real,
                   int* __restrict__ order, int* __restrict__ offsets,
                   int* __restrict__ tile_expert, int* __restrict__ tile_row0, int max_tiles,
                   int* __restrict__ cursor /* [E] scratch */) {
@@ -86,7 +104,8 @@ route_sort_kernel(const int* __restrict__ idx, int n_slots, int n_experts,
         for (int e = 0; e < n_experts; ++e) {
             const int c = cursor[e];
             offsets[e] = at;
-            for (int r = 0; r < c && tile < max_tiles; r += BM) {
+            // (an expert past n_real has no weights: its slots are settled where the sum is taken)
+            for (int r = 0; r < c && e < n_real && tile < max_tiles; r += BM) {
                 tile_expert[tile] = e;
                 tile_row0[tile] = at + r;
                 ++tile;
@@ -424,6 +443,8 @@ static inline bool takes_mma(int dtype, const void* a, const void* w, int K) {
 template <typename T>
 __global__ void expert_combine_kernel(const float* __restrict__ per_slot, int top,
                                       const void* __restrict__ shared, int shared_dtype,
+                                      const int* __restrict__ idx, const float* __restrict__ weight,
+                                      int n_real, const T* __restrict__ h,
                                       T* __restrict__ delta, size_t n, int d) {
     chain_release();
     chain_wait();
@@ -431,7 +452,13 @@ __global__ void expert_combine_kernel(const float* __restrict__ per_slot, int to
          i += (size_t)gridDim.x * blockDim.x) {
         const size_t t = i / d, c = i - t * d;
         float s = 0.f;
-        for (int j = 0; j < top; ++j) s += per_slot[(t * top + j) * d + c];
+        for (int j = 0; j < top; ++j) {
+            // a choice past the experts that have weights returns its input, times its weight
+            if (idx && idx[t * top + j] >= n_real)
+                s += weight[t * top + j] * Elem<T>::load(h + i);
+            else
+                s += per_slot[(t * top + j) * d + c];
+        }
         if (shared) s += load_as_float(shared, i, shared_dtype);
         Elem<T>::store(delta + i, s);
     }
@@ -441,20 +468,22 @@ __global__ void expert_combine_kernel(const float* __restrict__ per_slot, int to
 MLS_API int mls_expert_tile_rows() { return BM; }
 
 MLS_API int mls_route_topk(const float* logits, int n_tokens, int n_experts, int top, int renorm,
-                           int* idx, float* weight, cudaStream_t stream) {
+                           int softmax, const float* correction, float renorm_eps, int* idx,
+                           float* weight, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (top <= 0 || top > n_experts) return MLS_ERR_UNSUPPORTED;
     MLS_LAUNCH((route_topk_kernel), dim3((n_tokens + 3) / 4), dim3(128), 0, stream, logits,
-               n_tokens, n_experts, top, renorm, idx, weight);
+               n_tokens, n_experts, top, renorm, softmax, correction, renorm_eps, idx, weight);
     return launch_status();
 }
 
-MLS_API int mls_route_sort(const int* idx, int n_slots, int n_experts, int* order, int* offsets,
+MLS_API int mls_route_sort(const int* idx, int n_slots, int n_experts, int n_real, int* order,
+                           int* offsets,
                            int* tile_expert, int* tile_row0, int max_tiles, int* cursor,
                            cudaStream_t stream) {
     if (n_slots <= 0) return 0;
-    MLS_LAUNCH((route_sort_kernel), dim3(1), dim3(1024), 0, stream, idx, n_slots, n_experts, order,
-               offsets, tile_expert, tile_row0, max_tiles, cursor);
+    MLS_LAUNCH((route_sort_kernel), dim3(1), dim3(1024), 0, stream, idx, n_slots, n_experts,
+               n_real, order, offsets, tile_expert, tile_row0, max_tiles, cursor);
     return launch_status();
 }
 
@@ -509,7 +538,8 @@ MLS_API int mls_expert_down(const void* y, const void* w_down, float* per_slot, 
 }
 
 MLS_API int mls_expert_combine(const float* per_slot, int top, const void* shared,
-                               int shared_dtype, void* delta, int dtype, int n_tokens, int d,
+                               int shared_dtype, const int* idx, const float* weight, int n_real,
+                               const void* h, void* delta, int dtype, int n_tokens, int d,
                                cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     const size_t n = (size_t)n_tokens * d;
@@ -517,9 +547,11 @@ MLS_API int mls_expert_combine(const float* per_slot, int top, const void* share
     const int blocks = (int)(want < (size_t)(8 * sm_count()) ? want : 8 * sm_count());
     if (dtype == MLS_BF16)
         MLS_LAUNCH((expert_combine_kernel<__nv_bfloat16>), dim3(blocks), dim3(256), 0, stream,
-                   per_slot, top, shared, shared_dtype, (__nv_bfloat16*)delta, n, d);
+                   per_slot, top, shared, shared_dtype, idx, weight, n_real, (const __nv_bfloat16*)h,
+                   (__nv_bfloat16*)delta, n, d);
     else
         MLS_LAUNCH((expert_combine_kernel<float>), dim3(blocks), dim3(256), 0, stream, per_slot,
-                   top, shared, shared_dtype, (float*)delta, n, d);
+                   top, shared, shared_dtype, idx, weight, n_real, (const float*)h, (float*)delta,
+                   n, d);
     return launch_status();
 }

@@ -18,6 +18,12 @@
 //   (W [H, N, K], K contiguous), rows and heads of in / out at given strides; float32
 //   accumulation over k ascending, whatever T is: a token's result does not depend on
 //   its batch.
+//
+// mls_latent_rope_prep: the variant whose heads carry, beside the part that meets the latent,
+//   a rotated part that meets one rotated key part shared by all heads: the cached row is
+//   [latent | rotated key part], a query row [W_uk^T q_plain | rotated q part], and the same
+//   multi-query attention runs over rows of that width; its result's first r entries are the
+//   weighted latent.  mls_sigmoid_gate: the heads' outputs times sigmoid(gate).
 #include "common.cuh"
 #include "page_tail.cuh"
 
@@ -54,6 +60,109 @@ latent_norm_store_kernel(const float* __restrict__ down, int rq, int r, int rp,
         Elem<T>::store(dst + c, c < r ? row[rq + c] * inv * load_as_float(wkv, c, w_dtype) : 0.f);
     clear_page_tail<T>(page_tail_to_clear(slot_map, t, gridDim.x, slot, block_size), slot,
                        block_size, pool_slots / block_size, 1, rp, pool, pool);
+}
+
+
+// Values of a projection's row that may still lie in the parts of a cut along K.
+struct RowParts {
+    const float* base;             // [n_parts][T, width]
+    int n_parts;
+    long long part_stride;
+    int width;
+    __device__ __forceinline__ float at(int t, int col) const {
+        const float* p = base + (size_t)t * width + col;
+        float v = 0.f;
+        for (int k = 0; k < n_parts; ++k) v += p[(size_t)k * part_stride];
+        return v;
+    }
+};
+
+// Entry i of a vector of n entries whose first `dims` turn, entry j with entry j + dims/2
+// (j < dims/2), by the angle position * freq[j]; the others pass.  get(j) reads entry j.
+template <typename Get>
+__device__ __forceinline__ float rotated_entry(Get get, int i, int dims, int position,
+                                               const double* __restrict__ freq) {
+    const int half = dims >> 1;
+    if (i >= dims) return get(i);
+    const int j = i < half ? i : i - half;
+    float c, s;
+    angle_cos_sin(position, freq[j], c, s);
+    const float u = get(j), v = get(j + half);
+    return i < half ? u * c - v * s : v * c + u * s;
+}
+
+// One block a token.  From the float32 projection row [q heads (e plain | g turned) ... |
+// r + g down-projected entries]:
+//   q_plain[t, h, :e]                    the plain part of every head, as it is
+//   q_in[t, h * rp + r + i]              the turned part of every head, rotated (i < g);
+//                                        q_in[t, h * rp + r + g ..] = 0 up to rp
+//   pool[slot] = [unit_rms(down[:r]) * w | rotate(down[r : r + g]) | 0 ...]   (has_kv only)
+// and the rest of a page the request enters is cleared.
+template <typename T>
+__global__ void __launch_bounds__(LT_THREADS)
+latent_rope_prep_kernel(const RowParts proj, int q_col, int kv_col, int n_heads, int e, int g,
+                        int r, int rp, int rot_dims, const double* __restrict__ freq,
+                        const int* __restrict__ positions, const void* __restrict__ wkv,
+                        int w_dtype, float eps, T* __restrict__ q_plain, T* __restrict__ q_in,
+                        int q_in_width, int has_kv, const int* __restrict__ slot_map,
+                        T* __restrict__ pool, int block_size, int pool_slots, int* status) {
+    chain_release();
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const int slot = has_kv ? slot_map[t] : -1;
+    const int tail = has_kv ? page_tail_to_clear(slot_map, t, gridDim.x, slot, block_size) : 0;
+    chain_wait();
+    __shared__ float scratch[33];
+    const int hw = e + g;
+    for (int u = threadIdx.x; u < n_heads * e; u += LT_THREADS) {
+        const int h = u / e, i = u - h * e;
+        Elem<T>::store(q_plain + (size_t)t * n_heads * e + u, proj.at(t, q_col + h * hw + i));
+    }
+    const int turned = rp - r;                       // g rotated entries, then zeros
+    for (int u = threadIdx.x; u < n_heads * turned; u += LT_THREADS) {
+        const int h = u / turned, i = u - h * turned;
+        float v = 0.f;
+        if (i < g)
+            v = rotated_entry([&](int j) { return proj.at(t, q_col + h * hw + e + j); }, i,
+                              rot_dims, pos, freq);
+        Elem<T>::store(q_in + (size_t)t * q_in_width + (size_t)h * rp + r + i, v);
+    }
+    if (!has_kv) return;
+    const bool slot_ok = slot >= 0 && slot < pool_slots;
+    if (!slot_ok && threadIdx.x == 0 && status) atomicOr(status, MLS_STATUS_BAD_SLOT);
+    float s = 0.f;
+    for (int c = threadIdx.x; c < r; c += LT_THREADS) {
+        const float v = proj.at(t, kv_col + c);
+        s = fmaf(v, v, s);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(s, scratch) / (float)r + eps);
+    if (!slot_ok) return;
+    T* dst = pool + (size_t)slot * rp;
+    for (int c = threadIdx.x; c < rp; c += LT_THREADS) {
+        float v = 0.f;
+        if (c < r)
+            v = proj.at(t, kv_col + c) * inv * load_as_float(wkv, c, w_dtype);
+        else if (c < r + g)
+            v = rotated_entry([&](int j) { return proj.at(t, kv_col + r + j); }, c - r, rot_dims,
+                              pos, freq);
+        Elem<T>::store(dst + c, v);
+    }
+    clear_page_tail<T>(tail, slot, block_size, pool_slots / block_size, 1, rp, pool, pool);
+}
+
+// o[t, c] *= sigmoid(gate[t, gate_col + c]), the gate read from a float32 projection row.
+template <typename T>
+__global__ void __launch_bounds__(256)
+sigmoid_gate_kernel(T* __restrict__ o, const RowParts proj, int gate_col, int n_tokens, int n) {
+    chain_release();
+    chain_wait();
+    const size_t total = (size_t)n_tokens * n;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const int t = (int)(idx / n), c = (int)(idx - (size_t)t * n);
+        const float z = proj.at(t, gate_col + c);
+        Elem<T>::store(o + idx, Elem<T>::load(o + idx) / (1.0f + expf(-z)));
+    }
 }
 
 constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;   // 256 threads
@@ -148,5 +257,47 @@ MLS_API int mls_headwise_linear(const void* in, long long in_row, long long in_h
         MLS_LAUNCH((headwise_linear_kernel<float>), dim3(grid), dim3(256), 0, stream,
                    (const float*)in, in_row, in_head, (const float*)W, (float*)out, out_row,
                    out_head, n_tokens, N, K);
+    return launch_status();
+}
+
+MLS_API int mls_latent_rope_prep(const float* proj, int n_parts, long long part_stride,
+                                 int proj_width, int q_col, int kv_col, int n_tokens, int n_heads,
+                                 int e, int g, int r, int rp, int rot_dims, const double* freq,
+                                 const int* positions, const void* wkv, int w_dtype, float eps,
+                                 void* q_plain, void* q_in, int q_in_width, int dtype, int has_kv,
+                                 const int* slot_map, void* pool, int block_size,
+                                 long long pool_slots, int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (r <= 0 || g < 0 || rp < r + g || e < 0 || n_heads <= 0 || n_parts < 1 || rot_dims < 0 ||
+        rot_dims > g || (rot_dims & 1) || (rot_dims > 0 && !freq) || (has_kv && block_size <= 0))
+        return MLS_ERR_UNSUPPORTED;
+    const RowParts rows{proj, n_parts, part_stride, proj_width};
+    if (dtype == MLS_BF16)
+        MLS_LAUNCH((latent_rope_prep_kernel<__nv_bfloat16>), dim3(n_tokens), dim3(LT_THREADS), 0,
+                   stream, rows, q_col, kv_col, n_heads, e, g, r, rp, rot_dims, freq, positions, wkv,
+                   w_dtype, eps, (__nv_bfloat16*)q_plain, (__nv_bfloat16*)q_in, q_in_width, has_kv,
+                   slot_map, (__nv_bfloat16*)pool, block_size, (int)pool_slots, status);
+    else
+        MLS_LAUNCH((latent_rope_prep_kernel<float>), dim3(n_tokens), dim3(LT_THREADS), 0, stream,
+                   rows, q_col, kv_col, n_heads, e, g, r, rp, rot_dims, freq, positions, wkv, w_dtype,
+                   eps, (float*)q_plain, (float*)q_in, q_in_width, has_kv, slot_map, (float*)pool,
+                   block_size, (int)pool_slots, status);
+    return launch_status();
+}
+
+MLS_API int mls_sigmoid_gate(void* o, int dtype, const float* proj, int n_parts,
+                             long long part_stride, int proj_width, int gate_col, int n_tokens,
+                             int n, cudaStream_t stream) {
+    if (n_tokens <= 0 || n <= 0) return 0;
+    if (n_parts < 1) return MLS_ERR_UNSUPPORTED;
+    const RowParts rows{proj, n_parts, part_stride, proj_width};
+    const size_t want = ((size_t)n_tokens * n + 255) / 256;
+    const int blocks = (int)(want < (size_t)(8 * sm_count()) ? want : 8 * sm_count());
+    if (dtype == MLS_BF16)
+        MLS_LAUNCH((sigmoid_gate_kernel<__nv_bfloat16>), dim3(blocks), dim3(256), 0, stream,
+                   (__nv_bfloat16*)o, rows, gate_col, n_tokens, n);
+    else
+        MLS_LAUNCH((sigmoid_gate_kernel<float>), dim3(blocks), dim3(256), 0, stream, (float*)o, rows,
+                   gate_col, n_tokens, n);
     return launch_status();
 }

@@ -82,18 +82,32 @@ __global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ out
                                limit));
 }
 
-// Activations without a gate: out = act(in), element by element (in place allowed).
+// Activations without a gate: out = act(in + bias), element by element (in place allowed when
+// the types agree); `bias` [width] is optional and belongs to the columns of rows of `width`.
 // kind 0: the square of relu.
-template <typename T>
-__global__ void unary_act_kernel(const T* __restrict__ in, T* __restrict__ out, size_t n,
-                                 int kind) {
+template <typename TI, typename TO>
+__global__ void unary_act_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n,
+                                 int kind, const void* __restrict__ bias, int bias_dtype,
+                                 int width) {
     chain_release();
     chain_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
          i += (size_t)gridDim.x * blockDim.x) {
-        const float z = fmaxf(Elem<T>::load(in + i), 0.f);
-        Elem<T>::store(out + i, z * z);
+        float z = Elem<TI>::load(in + i);
+        if (bias) z += load_as_float(bias, i % width, bias_dtype);
+        z = fmaxf(z, 0.f);
+        Elem<TO>::store(out + i, z * z);
     }
+}
+
+// x = cap * tanh(x / cap) on float32 values.
+__global__ void softcap_f32_kernel(float* __restrict__ x, size_t n, float cap) {
+    chain_release();
+    chain_wait();
+    const float inv = 1.0f / cap;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (size_t)gridDim.x * blockDim.x)
+        x[i] = cap * tanhf(x[i] * inv);
 }
 
 __global__ void scale_f32_kernel(float* __restrict__ x, size_t n, float scale) {
@@ -105,19 +119,36 @@ __global__ void scale_f32_kernel(float* __restrict__ x, size_t n, float scale) {
 }
 }  // namespace
 
-// out[i] = relu(in[i])^2 (kind 0; other kinds are refused).
-MLS_API int mls_unary_act(const void* in, void* out, int dtype, long long n, int kind,
+// out[i] = relu(in[i] + bias[i % width])^2 (kind 0; other kinds are refused).  `in` is of type
+// `in_dtype`, `out` of `dtype`; a float32 input with a bfloat16 output is the one mixed pair.
+MLS_API int mls_unary_act(const void* in, int in_dtype, void* out, int dtype, long long n,
+                          int kind, const void* bias, int bias_dtype, int width,
                           cudaStream_t stream) {
     if (n <= 0) return 0;
-    if (kind != 0) return MLS_ERR_UNSUPPORTED;
+    if (kind != 0 || (bias && width <= 0)) return MLS_ERR_UNSUPPORTED;
+    if (in_dtype != dtype && !(in_dtype == MLS_F32 && dtype == MLS_BF16)) return MLS_ERR_UNSUPPORTED;
     const long long want = (n + 255) / 256;
     const int blocks = (int)(want < 16LL * sm_count() ? want : 16LL * sm_count());
-    if (dtype == MLS_BF16)
-        MLS_LAUNCH((unary_act_kernel<__nv_bfloat16>), dim3(blocks), dim3(256), 0, stream,
-                   (const __nv_bfloat16*)in, (__nv_bfloat16*)out, (size_t)n, kind);
+    if (dtype == MLS_BF16 && in_dtype == MLS_BF16)
+        MLS_LAUNCH((unary_act_kernel<__nv_bfloat16, __nv_bfloat16>), dim3(blocks), dim3(256), 0,
+                   stream, (const __nv_bfloat16*)in, (__nv_bfloat16*)out, (size_t)n, kind, bias,
+                   bias_dtype, width);
+    else if (dtype == MLS_BF16)
+        MLS_LAUNCH((unary_act_kernel<float, __nv_bfloat16>), dim3(blocks), dim3(256), 0, stream,
+                   (const float*)in, (__nv_bfloat16*)out, (size_t)n, kind, bias, bias_dtype, width);
     else
-        MLS_LAUNCH((unary_act_kernel<float>), dim3(blocks), dim3(256), 0, stream,
-                   (const float*)in, (float*)out, (size_t)n, kind);
+        MLS_LAUNCH((unary_act_kernel<float, float>), dim3(blocks), dim3(256), 0, stream,
+                   (const float*)in, (float*)out, (size_t)n, kind, bias, bias_dtype, width);
+    return launch_status();
+}
+
+// x[i] = cap * tanh(x[i] / cap) on float32 values (capped logits).
+MLS_API int mls_softcap_f32(float* x, long long n, float cap, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (!(cap > 0.f)) return MLS_ERR_UNSUPPORTED;
+    const long long want = (n + 255) / 256;
+    const int blocks = (int)(want < 16LL * sm_count() ? want : 16LL * sm_count());
+    MLS_LAUNCH((softcap_f32_kernel), dim3(blocks), dim3(256), 0, stream, x, (size_t)n, cap);
     return launch_status();
 }
 

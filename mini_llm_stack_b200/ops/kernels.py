@@ -132,10 +132,11 @@ class Ops:
                                   _LL, _I, _P, _I, _LL, _P, _P])
         self._attention_simt = _decl(core, "mls_attention_simt",
                                      [_P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I,
-                                      _I, _F, _I, _F, _LL, _P])
+                                      _I, _F, _I, _F, _LL, _P, _P])
         self._swiglu = _decl(core, "mls_swiglu", [_P, _P, _I, _I, _I, _P])
         self._clamped_glu = _decl(core, "mls_clamped_glu", [_P, _P, _I, _I, _I, _F, _F, _P])
-        self._unary_act = _decl(core, "mls_unary_act", [_P, _P, _I, _LL, _I, _P])
+        self._unary_act = _decl(core, "mls_unary_act", [_P, _I, _P, _I, _LL, _I, _P, _I, _I, _P])
+        self._softcap_f32 = _decl(core, "mls_softcap_f32", [_P, _LL, _F, _P])
         self._scale_f32 = _decl(core, "mls_scale_f32", [_P, _LL, _F, _P])
         self._part_libs: dict = {}               # kernels of parts only some models have
         self._sample = _decl(core, "mls_sample", [_P, _P, _P, _P, _I, _I, _P, _P])
@@ -226,6 +227,10 @@ class Ops:
         """(pointer, type code, parts, part stride) of a pending residual delta."""
         if delta is None:
             return None, 0, 1, 0
+        if hasattr(delta, "resolve"):
+            # a delta that still has a map to go through, met by a consumer that does not
+            # apply it itself: the map runs as a kernel of its own
+            delta = delta.resolve()
         if isinstance(delta, SplitParts):
             parts = delta.parts
             _need(parts.shape[1:] == (t, d) and parts.is_contiguous()
@@ -446,8 +451,9 @@ class Ops:
         """Whether a product and an ungated activation of its outputs can run as one kernel."""
         return (self.act_dtype == torch.bfloat16 and self.gemm_impl != "cublas" and k % 8 == 0)
 
-    def linear_relu_squared(self, a, w, out) -> None:
-        """``out[M, N] = relu(a @ w^T)^2`` in one kernel (the tcgen05 product's epilogue)."""
+    def linear_relu_squared(self, a, w, out, bias=None) -> None:
+        """``out[M, N] = relu(a @ w^T + bias)^2``; without a bias in one kernel (the tcgen05
+        product's epilogue), with one as the product in float32 and the activation on it."""
         m, k = a.shape
         n = w.shape[0]
         _need(w.shape == (n, k) and out.shape == (m, n) and a.dtype == torch.bfloat16
@@ -455,6 +461,11 @@ class Ops:
         _need(a.is_contiguous() and w.is_contiguous() and out.is_contiguous(),
               "linear_relu_squared: operands must be contiguous")
         if m == 0:
+            return
+        if bias is not None:
+            z = self.scratch("biased_product", m * n)[:m * n].view(m, n)
+            self.linear(a, w, z)
+            self.relu_squared(z, out, bias=bias)
             return
         self._gemm_bf16(a, w, out, m, n, k, epilogue=2)
 
@@ -503,10 +514,10 @@ class Ops:
             lib = self._load("attention", {"MLS_HEAD_DIM": int(hd)})
             fn = _decl(lib, "mls_attention_mma",
                        [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _F, _I, _I, _I,
-                        _P, _P, _LL, _P, _I, _P])
+                        _P, _P, _LL, _P, _I, _P, _P])
             tc = _decl(lib, "mls_attention_tc",
                        [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _F, _I, _I, _I, _LL,
-                        _P, _P])
+                        _P, _P, _P])
             fused = _decl(lib, "mls_attention_decode_fused",
                           [_P, _I, _LL, _P, _P, _P, _I, _P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I,
                            _I, _I, _F, _I, _I, _P, _P, _LL, _P, _P])
@@ -557,15 +568,19 @@ class Ops:
                 "tensor_cores": self.attention_tensor_cores(hd)}
 
     def paged_attention(self, qkv, out, cache, step, n_heads: int, n_kv: int, hd: int,
-                        scale: float, window: int, plan=None, softcap: float = 0.0) -> None:
+                        scale: float, window: int, plan=None, softcap: float = 0.0,
+                        sink=None) -> None:
         """Attention of the step's tokens over the pages.  ``softcap`` c > 0: scores become
-        ``c * tanh(score / c)`` before the softmax.  ``plan`` (the mixer's, from
+        ``c * tanh(score / c)`` before the softmax.  ``sink`` (float32 [n_heads]): the softmax's
+        denominator of head h also holds ``exp(sink[h])``, a term without key or value.  ``plan`` (the mixer's, from
         ``attention_facts``): ``n_tiles`` / ``n_tiles_tc`` / ``n_tiles_tc_wide`` tiles of the
         requests that are not small, ``any_small``, ``n_split`` context splits for the small ones."""
         g = step.groups[cache.group]
         t = step.n_tokens
         _need(out.shape == (t, n_heads * hd) and out.is_contiguous(), "attention: bad out")
         _need(cache.k_pool.dtype == qkv.dtype, "attention: cache and activations differ")
+        _need(sink is None or (sink.dtype == torch.float32 and sink.shape == (n_heads,)
+                               and sink.is_contiguous()), "attention: sinks are float32 [heads]")
         if self.attention_tensor_cores(hd) and qkv.dtype == torch.bfloat16:
             fns = self._attention_libs.get(hd)
             _need(fns is not None, f"attention kernels for head size {hd} were not required")
@@ -582,7 +597,7 @@ class Ops:
                           _ptr(g.block_table), g.max_blocks, _ptr(step.cu_q), _ptr(step.ctx_len),
                           step.n_requests, n_heads, n_kv, g.block_size, float(scale), int(window),
                           float(softcap), n_tiles_tc, plan.n_tiles_tc_wide, n_small, cache.k_pool.shape[1],
-                          _ptr(self.status), self._stream()), "attention_tc")
+                          _ptr(self.status), _ptr(sink), self._stream()), "attention_tc")
                 n_tiles = 0
                 if not n_small:
                     return
@@ -601,7 +616,7 @@ class Ops:
                       step.n_requests, t, n_heads, n_kv, g.block_size, float(scale), int(window),
                       float(softcap), n_tiles, n_small, n_split, _ptr(part_o), _ptr(part_lse),
                       cache.k_pool.shape[1], _ptr(self.status),
-                      0 if self.attention_impl == "no_tma" else 1, self._stream()),
+                      0 if self.attention_impl == "no_tma" else 1, _ptr(sink), self._stream()),
                    "attention_mma")
             return
         self.launches += 1
@@ -609,7 +624,7 @@ class Ops:
             _ptr(qkv), _ptr(out), _code(qkv.dtype), _ptr(cache.k_pool), _ptr(cache.v_pool),
             _ptr(g.block_table), g.max_blocks, _ptr(step.positions), _ptr(step.req_of_token),
             t, n_heads, n_kv, hd, g.block_size, float(scale), int(window), float(softcap),
-            cache.k_pool.shape[1], self._stream()), "attention_simt")
+            cache.k_pool.shape[1], _ptr(sink), self._stream()), "attention_simt")
 
     def _split_launches(self, n_split: int, tma: bool, n_ctas: int) -> int:
         """Kernels the context-split attention launches: two to eight splits merge inside
@@ -672,13 +687,23 @@ class Ops:
         _check(self._swiglu(_ptr(gu), _ptr(out), _code(out.dtype), t, inter, self._stream()),
                "swiglu")
 
-    def relu_squared(self, z, out) -> None:
-        """``out = relu(z)^2`` element by element (``out`` may be ``z``)."""
-        _need(z.shape == out.shape and z.dtype == out.dtype and z.is_contiguous()
-              and out.is_contiguous(), "relu_squared: operands")
+    def relu_squared(self, z, out, bias=None) -> None:
+        """``out = relu(z + bias)^2`` element by element (``out`` may be ``z``; a float32 ``z``
+        may go to a bfloat16 ``out``); ``bias`` [columns] is optional."""
+        _need(z.shape == out.shape and z.is_contiguous() and out.is_contiguous()
+              and (z.dtype == out.dtype or z.dtype == torch.float32), "relu_squared: operands")
+        _need(bias is None or (bias.shape == (z.shape[-1],) and bias.is_contiguous()),
+              "relu_squared: bad bias")
         self.launches += 1
-        _check(self._unary_act(_ptr(z), _ptr(out), _code(z.dtype), z.numel(), 0, self._stream()),
-               "relu_squared")
+        _check(self._unary_act(_ptr(z), _code(z.dtype), _ptr(out), _code(out.dtype), z.numel(), 0,
+                               _ptr(bias), _code(bias.dtype) if bias is not None else 0,
+                               z.shape[-1], self._stream()), "relu_squared")
+
+    def softcap_(self, x, cap: float) -> None:
+        """``x = cap * tanh(x / cap)`` on float32 values."""
+        _need(x.dtype == torch.float32 and x.is_contiguous() and cap > 0, "softcap_: float32 values")
+        self.launches += 1
+        _check(self._softcap_f32(_ptr(x), x.numel(), float(cap), self._stream()), "softcap_")
 
     def scale_(self, x, scale: float) -> None:
         """``x *= scale`` on float32 values."""
@@ -705,7 +730,16 @@ class Ops:
                                        [_P, _I, _I, _I, _I, _P, _P, _I, _F, _P, _I, _P, _P, _I,
                                         _LL, _P, _P]),
                    "headwise": _decl(lib, "mls_headwise_linear",
-                                     [_P, _LL, _LL, _P, _P, _LL, _LL, _I, _I, _I, _I, _I, _P])}
+                                     [_P, _LL, _LL, _P, _P, _LL, _LL, _I, _I, _I, _I, _I, _P]),
+                   "rope_prep": _decl(lib, "mls_latent_rope_prep",
+                                      [_P, _I, _LL, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P,
+                                       _P, _I, _F, _P, _P, _I, _I, _I, _P, _P, _I, _LL, _P, _P]),
+                   "gate": _decl(lib, "mls_sigmoid_gate",
+                                 [_P, _I, _P, _I, _LL, _I, _I, _I, _I, _P])}
+        elif name == "tanhnorm":
+            fns = {"add_tanh_norm": _decl(lib, "mls_add_tanh_norm",
+                                          [_P, _P, _I, _I, _LL, _P, _F, _P, _P, _P, _F, _P, _P, _I,
+                                           _P, _I, _P, _P, _I, _I, _P])}
         elif name == "mlstm":
             fns = {"columns": _decl(lib, "mls_mlstm_columns", [_I, _I]),
                    "scan": _decl(lib, "mls_mlstm_scan",
@@ -715,14 +749,16 @@ class Ops:
                                    [_P, _P, _P, _I, _I, _P, _I, _F, _P, _I, _I, _I, _I, _P])}
         elif name == "experts":
             fns = {"tile_rows": _decl(lib, "mls_expert_tile_rows", []),
-                   "topk": _decl(lib, "mls_route_topk", [_P, _I, _I, _I, _I, _P, _P, _P]),
-                   "sort": _decl(lib, "mls_route_sort", [_P, _I, _I, _P, _P, _P, _P, _I, _P, _P]),
+                   "topk": _decl(lib, "mls_route_topk",
+                                 [_P, _I, _I, _I, _I, _I, _P, _F, _P, _P, _P]),
+                   "sort": _decl(lib, "mls_route_sort",
+                                 [_P, _I, _I, _I, _P, _P, _P, _P, _I, _P, _P]),
                    "glu": _decl(lib, "mls_expert_glu",
                                 [_P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _P]),
                    "down": _decl(lib, "mls_expert_down",
                                  [_P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _P]),
                    "combine": _decl(lib, "mls_expert_combine",
-                                    [_P, _I, _P, _I, _P, _I, _I, _I, _P])}
+                                    [_P, _I, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _P])}
         elif name == "shortconv":
             fns = {"qk": _decl(lib, "mls_qk_conv_norm_rope_store",
                                [_P, _I, _LL, _P, _P, _I, _P, _P, _I, _F, _P, _LL, _I, _P, _P, _P, _P,
@@ -894,17 +930,25 @@ class Ops:
             _code(weight.dtype), float(eps), _ptr(out), _code(out.dtype), t, n_heads, f,
             self._stream()), "mlstm_finish")
 
-    def route(self, logits, top: int, renorm: bool, work: dict) -> None:
-        """Choose and sort: from float32 router ``logits [T, E]`` the ``top`` experts a
-        token with sigmoid scores as weights, then the (token, choice) slots ordered by
-        expert.  ``work`` holds the int32 / float32 arrays (``expert_work``)."""
+    def route(self, logits, top: int, renorm: bool, work: dict, softmax: bool = False,
+              correction=None, renorm_eps: float = 0.0, n_real=None) -> None:
+        """Choose and sort: from float32 router ``logits [T, E]`` the ``top`` outputs a token
+        with the largest score (sigmoid, or ``softmax`` over all outputs) plus ``correction``
+        (float32 [E], in the choice only), the scores themselves as weights (``renorm``:
+        divided by their sum + ``renorm_eps``), then the (token, choice) slots ordered by
+        expert.  Outputs from ``n_real`` on stand for experts without weights and get no
+        tiles.  ``work`` holds the int32 / float32 arrays (``expert_work``)."""
         t, n_experts = logits.shape
         _need(logits.dtype == torch.float32 and logits.is_contiguous(), "route: logits")
+        _need(correction is None or (correction.dtype == torch.float32 and correction.is_contiguous()
+                                     and correction.shape == (n_experts,)), "route: correction")
         fns = self._part_lib("experts")
         self.launches += 2
         _check(fns["topk"](_ptr(logits), t, n_experts, top, 1 if renorm else 0,
+                           1 if softmax else 0, _ptr(correction), float(renorm_eps),
                            _ptr(work["idx"]), _ptr(work["weight"]), self._stream()), "route_topk")
-        _check(fns["sort"](_ptr(work["idx"]), t * top, n_experts, _ptr(work["order"]),
+        _check(fns["sort"](_ptr(work["idx"]), t * top, n_experts,
+                           n_experts if n_real is None else int(n_real), _ptr(work["order"]),
                            _ptr(work["offsets"]), _ptr(work["tile_expert"]),
                            _ptr(work["tile_row0"]), work["max_tiles"], _ptr(work["cursor"]),
                            self._stream()), "route_sort")
@@ -946,16 +990,113 @@ class Ops:
             work["max_tiles"], _ptr(work["weight"]), top, 1 if scale_out else 0, d, f,
             self._many_rows(y.shape[0], n_experts), self._stream()), "expert_down")
 
-    def expert_combine(self, per_slot, top: int, shared, delta) -> None:
-        """``delta[t] = sum_j per_slot[t * top + j] + shared[t]``."""
+    def expert_combine(self, per_slot, top: int, shared, delta, work=None, n_real=None,
+                       h=None) -> None:
+        """``delta[t] = sum_j per_slot[t * top + j] + shared[t]``; with ``n_real`` a choice of
+        an output from ``n_real`` on adds ``weight * h[t]`` instead (an expert that returns
+        its input)."""
         t, d = delta.shape
         _need(per_slot.shape == (t * top, d) and delta.is_contiguous(), "expert_combine: shapes")
         _need(shared is None or (shared.shape == (t, d) and shared.is_contiguous()),
               "expert_combine: bad shared addend")
+        idx = weight = None
+        if n_real is not None:
+            _need(work is not None and h is not None and h.shape == (t, d) and h.is_contiguous()
+                  and h.dtype == delta.dtype, "expert_combine: identity experts need h and the routing")
+            idx, weight = work["idx"], work["weight"]
         self.launches += 1
         _check(self._part_lib("experts")["combine"](
             _ptr(per_slot), top, _ptr(shared), _code(shared.dtype) if shared is not None else 0,
+            _ptr(idx), _ptr(weight), int(n_real or 0), _ptr(h),
             _ptr(delta), _code(delta.dtype), t, d, self._stream()), "expert_combine")
+
+    def add_tanh_norm(self, x, delta, norm, h, post=None, bias=None, rows=None, n_rows: int = 0,
+                      y_out=None) -> None:
+        """The norm without statistics, ``n(v) = tanh(alpha v) * w + b``, in the pass that adds a
+        sublayer's output to the stream: ``y = delta (+ bias)``; with ``post = (alpha, w, b,
+        scale)`` ``y = n_post(y) * scale`` (``scale`` may be None); ``x += y``;
+        ``h = n(x)`` with ``norm = (alpha, w, b)``.  ``delta``: a tensor, ``SplitParts`` or None.
+        With ``rows`` only those rows are read and ``x`` stays as it is.  ``x`` None and ``h``
+        None with ``y_out`` (float32): only the mapped delta is written."""
+        src = x if x is not None else y_out
+        t, d = src.shape
+        n_out = t if rows is None else n_rows
+        _need(x is None or (x.dtype == torch.float32 and x.is_contiguous()),
+              "add_tanh_norm: x must be float32")
+        _need(h is None or (h.shape == (n_out, d) and h.is_contiguous()), "add_tanh_norm: bad output")
+        _need(y_out is None or (y_out.shape == (n_out, d) and y_out.dtype == torch.float32
+                                and y_out.is_contiguous()), "add_tanh_norm: bad mapped output")
+        vecs = [v for v in ((norm or ())[1:] + (tuple(post[1:]) if post else ()) + (bias,))
+                if v is not None]
+        _need(all(v.shape == (d,) and v.is_contiguous() and v.dtype == vecs[0].dtype for v in vecs),
+              "add_tanh_norm: vectors of one type and of the row's width")
+        _need(rows is None or (rows.dtype == torch.int32 and rows.numel() >= n_rows),
+              "add_tanh_norm: bad row indices")
+        dp, dcode, parts, stride = self._delta_args(delta, t, d, "add_tanh_norm")
+        p_alpha, p_w, p_b, p_s = post if post else (0.0, None, None, None)
+        alpha, w, b = norm if norm else (0.0, None, None)
+        self.launches += 1
+        _check(self._part_lib("tanhnorm")["add_tanh_norm"](
+            _ptr(x), dp, dcode, parts, stride, _ptr(bias), float(p_alpha), _ptr(p_w), _ptr(p_b),
+            _ptr(p_s), float(alpha), _ptr(w), _ptr(b), _code(vecs[0].dtype) if vecs else 0,
+            _ptr(h), _code(h.dtype) if h is not None else 0, _ptr(y_out), _ptr(rows), n_out, d,
+            self._stream()), "add_tanh_norm")
+        if isinstance(delta, SplitParts):
+            delta.release()
+
+    def _row_parts(self, proj, t: int, what: str):
+        """(pointer, parts, part stride, row width) of a float32 projection given as a tensor
+        ``[T, W]`` or as the ``SplitParts`` of its product."""
+        if isinstance(proj, SplitParts):
+            parts = proj.parts
+            _need(parts.dtype == torch.float32 and parts.is_contiguous() and parts.shape[1] == t,
+                  f"{what}: bad parts")
+            return parts.data_ptr(), parts.shape[0], t * parts.shape[2], parts.shape[2]
+        _need(proj.dtype == torch.float32 and proj.is_contiguous() and proj.shape[0] == t,
+              f"{what}: the projection must be float32 rows")
+        return proj.data_ptr(), 1, 0, proj.shape[1]
+
+    def latent_rope_prep(self, proj, q_col: int, kv_col: int, n_heads: int, e: int, g: int,
+                         r: int, rp: int, rot_dims: int, freq, w_kv, eps: float, q_plain, q_in,
+                         cache, step) -> None:
+        """From the float32 projection row ``[... q heads (e plain | g rotated) ... r + g
+        down-projected ...]`` (a tensor or ``SplitParts``): the heads' plain parts into
+        ``q_plain [T, H * e]``, their rotated parts into ``q_in[t, h * rp + r : + g]`` (zeros up
+        to ``rp``), and, if the call writes its cache, ``[unit_rms(down[:r]) * w_kv | rotated
+        down[r:] | 0]`` into the pool at the step's slots.  The first ``rot_dims`` of the g
+        entries turn, entry i with i + rot_dims/2, by ``position * freq[i]`` (float64)."""
+        t = step.n_tokens
+        ptr, n_parts, stride, width = self._row_parts(proj, t, "latent_rope_prep")
+        writes = bool(cache.writes)
+        pool = cache.k_pool
+        grp = step.groups[cache.group]
+        _need(q_plain.shape == (t, n_heads * e) and q_plain.is_contiguous()
+              and q_in.is_contiguous() and q_in.shape[0] == t and q_in.shape[1] >= n_heads * rp
+              and q_plain.dtype == q_in.dtype == pool.dtype, "latent_rope_prep: bad query buffers")
+        _need(pool.is_contiguous() and pool.shape[0] == 1 and pool.shape[3] == rp,
+              "latent_rope_prep: bad pool")
+        _need(rot_dims == 0 or (freq is not None and freq.dtype == torch.float64
+                                and freq.numel() >= rot_dims // 2), "latent_rope_prep: frequencies")
+        _need(not writes or w_kv.shape == (r,), "latent_rope_prep: bad norm weight")
+        self.launches += 1
+        _check(self._part_lib("latent")["rope_prep"](
+            ptr, n_parts, stride, width, q_col, kv_col, t, n_heads, e, g, r, rp, rot_dims,
+            _ptr(freq), _ptr(step.positions), _ptr(w_kv) if writes else None,
+            _code(w_kv.dtype) if writes else 0, float(eps), _ptr(q_plain), _ptr(q_in),
+            q_in.shape[1], _code(pool.dtype), 1 if writes else 0, _ptr(grp.slot_map), _ptr(pool),
+            grp.block_size, pool.shape[1] * pool.shape[2], _ptr(self.status), self._stream()),
+            "latent_rope_prep")
+
+    def sigmoid_gate(self, o, proj, gate_col: int) -> None:
+        """``o[t, c] *= sigmoid(proj[t, gate_col + c])``; ``proj`` a float32 tensor or the
+        ``SplitParts`` of its product."""
+        t, n = o.shape
+        ptr, n_parts, stride, width = self._row_parts(proj, t, "sigmoid_gate")
+        _need(o.is_contiguous() and gate_col + n <= width, "sigmoid_gate: operands")
+        self.launches += 1
+        _check(self._part_lib("latent")["gate"](
+            _ptr(o), _code(o.dtype), ptr, n_parts, stride, width, gate_col, t, n,
+            self._stream()), "sigmoid_gate")
 
     def settle_concat(self, x, delta, other, out) -> None:
         """``x += delta`` (a tensor, ``SplitParts`` or None), then ``out[t] = [x[t] | other[t]]``

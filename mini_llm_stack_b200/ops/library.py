@@ -43,6 +43,7 @@ MODULES = {
     "argmax_static": ["argmax_static.cu"],
     # parts only some architectures have: built when a model with such a part is loaded
     "layernorm": ["layernorm.cu"],
+    "tanhnorm": ["tanh_norm.cu"],
     "latent": ["latent.cu"],
     "mlstm": ["mlstm.cu"],
     "experts": ["experts.cu"],
@@ -59,8 +60,8 @@ def all_modules(head_sizes=()) -> list:
     if (CSRC / "gemm_tcgen05.cu").is_file():
         out.append(("gemm", {}))
     out.append(("argmax_static", {}))
-    out += [(name, {}) for name in ("layernorm", "latent", "mlstm", "experts", "shortconv",
-                                    "scan")]
+    out += [(name, {}) for name in ("layernorm", "tanhnorm", "latent", "mlstm", "experts",
+                                    "shortconv", "scan")]
     return out
 
 

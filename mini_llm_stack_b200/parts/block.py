@@ -1,4 +1,5 @@
-"""The arrangement of a layer's parts: the pre-norm residual block.
+"""The arrangement of a layer's parts: the pre-norm residual block, and the block with a norm
+before and behind every sublayer.
 
 Reference (train/model.py:200-217): ``x = x + mixer(norm_a(x))``;
 ``x = x + feed_forward(norm_b(x))``.  The block owns the order and the names
@@ -81,3 +82,59 @@ class PreNormBlock(Part):
             return
         h = self.ffn_norm.forward(stream)
         stream.push(self.ffn.forward(h, step))
+
+
+class SandwichBlock(PreNormBlock):
+    """A norm before and behind each sublayer, and an optional per-channel scale on what
+    joins the stream: ``x <- x + s1 * post1(mixer(pre1(x)))``; ``x <- x + s2 *
+    post2(ffn(pre2(x)))``.  The norms behind the sublayers are of a kind that can ride on the
+    pending delta (``norm.mapped(delta, scale, bias)``, e.g. ``DynamicTanhNorm``): they cost
+    no pass of their own.  A sublayer may return ``(delta, vector)``: the vector (an output
+    bias) is added to every row before the norm behind it.
+
+    ``names``: prefixes of (pre1, mixer, post1, pre2, ffn, post2); ``scale_names``: the two
+    scale vectors' tensor names, or None for a block without them."""
+
+    def __init__(self, mixer_norm, mixer, mixer_post, ffn_norm, ffn, ffn_post, d_model: int,
+                 names=("norm1", "mix", "norm1b", "norm2", "mlp", "norm2b"),
+                 scale_names=("ls1", "ls2")):
+        self.mixer_norm, self.mixer, self.mixer_post = mixer_norm, mixer, mixer_post
+        self.ffn_norm, self.ffn, self.ffn_post = ffn_norm, ffn, ffn_post
+        self.d_model = int(d_model)
+        self.names, self.scale_names = tuple(names), scale_names
+        self.scales = [None, None]
+
+    def _named_parts(self):
+        parts = (self.mixer_norm, self.mixer, self.mixer_post, self.ffn_norm, self.ffn,
+                 self.ffn_post)
+        return [(n, p) for n, p in zip(self.names, parts) if p is not None]
+
+    def tensor_specs(self) -> dict:
+        from .base import TensorSpec
+        out = super().tensor_specs()
+        if self.scale_names is not None:
+            out[self.scale_names[0]] = TensorSpec((self.d_model,), kind="vector", init="ones")
+            if self.ffn is not None:
+                out[self.scale_names[1]] = TensorSpec((self.d_model,), kind="vector", init="ones")
+        return out
+
+    def bind(self, tensors: dict, runtime) -> None:
+        super().bind(tensors, runtime)
+        if self.scale_names is not None:
+            self.scales = [tensors[n].contiguous() if n in tensors else None
+                           for n in self.scale_names]
+
+    @staticmethod
+    def _push(stream: ResidualStream, post, out, scale) -> None:
+        bias = None
+        if isinstance(out, tuple):
+            out, bias = out
+        stream.push(post.mapped(out, scale, bias))
+
+    def forward(self, stream: ResidualStream, step: StepContext, cache: CacheHandle) -> None:
+        h = self.mixer_norm.forward(stream)
+        self._push(stream, self.mixer_post, self.mixer.forward(h, step, cache), self.scales[0])
+        if self.ffn is None:
+            return
+        h = self.ffn_norm.forward(stream)
+        self._push(stream, self.ffn_post, self.ffn.forward(h, step), self.scales[1])

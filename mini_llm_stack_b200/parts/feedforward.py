@@ -107,24 +107,38 @@ class ClampedGLUFeedForward(FeedForward):
 
 
 class SquaredReluFeedForward(FeedForward):
-    """``W_down relu(W_up h)^2``: no gate, no biases.  The activation runs in float32, in
-    the projection's own epilogue where the tcgen05 kernel takes the sizes (as
-    ``SwiGLUFeedForward`` does), else on the projection's output."""
+    """``W_down relu(W_up h + b_up)^2 + b_down``: no gate; the biases (tensors ``<up>.b``,
+    ``<down>.b``) only with ``biases``.  The activation runs in float32, in the projection's
+    own epilogue where the tcgen05 kernel takes the sizes (as ``SwiGLUFeedForward`` does), else
+    on the projection's output (left in float32 where a bias is still to be added).  With
+    biases ``forward`` returns ``(delta, b_down)``: the block adds the vector to every row."""
 
     decode_capturable = prompt_capturable = True
 
-    def __init__(self, d_model: int, intermediate_size: int, names=("up", "down")):
+    def __init__(self, d_model: int, intermediate_size: int, names=("up", "down"),
+                 biases: bool = False):
         self.d_model, self.intermediate_size = int(d_model), int(intermediate_size)
-        self.names = tuple(names)
+        self.names, self.biases = tuple(names), bool(biases)
+        self.b_up = self.b_down = None
 
     def tensor_specs(self) -> dict:
         d, i = self.d_model, self.intermediate_size
-        return {self.names[0]: TensorSpec((i, d)), self.names[1]: TensorSpec((d, i))}
+        up, down = self.names
+        out = {up: TensorSpec((i, d))}
+        if self.biases:
+            out[f"{up}.b"] = TensorSpec((i,), kind="vector", init="zeros")
+        out[down] = TensorSpec((d, i))
+        if self.biases:
+            out[f"{down}.b"] = TensorSpec((d,), kind="vector", init="zeros")
+        return out
 
     def bind(self, tensors: dict, runtime) -> None:
         self.runtime = runtime
         self.w_up = runtime.ops.prepare_weight(tensors[self.names[0]])
         self.w_down = runtime.ops.prepare_weight(tensors[self.names[1]])
+        if self.biases:
+            self.b_up = tensors[f"{self.names[0]}.b"].contiguous()
+            self.b_down = tensors[f"{self.names[1]}.b"].contiguous()
         self.fused = (self.w_up.dtype == torch.bfloat16
                       and runtime.ops.can_fuse_activation(self.d_model))
 
@@ -133,40 +147,59 @@ class SquaredReluFeedForward(FeedForward):
         t = h.shape[0]
         act = rt.buffer("ffn_act", (t, self.intermediate_size), rt.act_dtype)
         if self.fused:
-            rt.ops.linear_relu_squared(h, self.w_up, act)
+            rt.ops.linear_relu_squared(h, self.w_up, act, bias=self.b_up)
+        elif self.b_up is not None:
+            z = rt.buffer("ffn_up", (t, self.intermediate_size), torch.float32)
+            rt.ops.linear(h, self.w_up, z)
+            rt.ops.relu_squared(z, act, bias=self.b_up)
         else:
             rt.ops.linear(h, self.w_up, act)
             rt.ops.relu_squared(act, act)
         delta = rt.buffer("delta", (t, self.d_model), rt.act_dtype)
-        return rt.ops.linear_parts(act, self.w_down, delta)
+        delta = rt.ops.linear_parts(act, self.w_down, delta)
+        return (delta, self.b_down) if self.b_down is not None else delta
 
 
 class RoutedExperts(FeedForward):
-    """A mixture of small SwiGLU experts with a sigmoid router.
+    """A mixture of small SwiGLU experts behind a float32 router.
 
-    Router logits ``z = W_r h`` and scores ``s = sigmoid(z)`` in float32; a token takes
-    its ``top`` experts with the largest scores (lowest index on a tie) and weighs them
-    by the scores themselves (``renormalise``: divided by their sum).  ``weigh`` says
-    where a weight multiplies: "input" (the expert sees ``w * h``) or "output".  A
-    ``shared`` feed-forward, if any, runs for every token and is added.  Tensors:
-    ``router`` [E, d] and ``e<i>.gate / up / down`` for every expert; the shared
-    part's under ``shared``."""
+    Router logits ``z = W_r h`` and scores ``s = sigmoid(z)`` or, with ``score="softmax"``,
+    ``softmax(z)`` over all router outputs, in float32; a token takes its ``top`` outputs
+    with the largest scores (lowest index on a tie; with ``correction`` the vector
+    ``correction`` [outputs] is added for the choice only) and weighs them by the scores
+    themselves (``renormalise``: divided by their sum + ``renorm_eps``).  ``weigh`` says
+    where a weight multiplies: "input" (the expert sees ``w * h``) or "output".  The last
+    ``identity`` router outputs stand for experts without tensors that return their input
+    (times the weight).  A ``shared`` feed-forward, if any, runs for every token and is
+    added.  Tensors: ``router`` [E + identity, d] and ``e<i>.gate / up / down`` for each of
+    the E experts; the shared part's under ``shared``."""
 
     decode_capturable = prompt_capturable = True   # routing, sorting and the products stay on the device
 
     def __init__(self, d_model: int, n_experts: int, top: int, expert_size: int, shared=None,
-                 weigh: str = "input", renormalise: bool = False):
+                 weigh: str = "input", renormalise: bool = False, score: str = "sigmoid",
+                 correction: bool = False, identity: int = 0, renorm_eps: float = 0.0):
         if weigh not in ("input", "output"):
             raise ValueError(f"weigh must be 'input' or 'output', not {weigh!r}")
-        if not 0 < int(top) <= int(n_experts):
-            raise ValueError("top must lie in 1..n_experts")
+        if score not in ("sigmoid", "softmax"):
+            raise ValueError(f"score must be 'sigmoid' or 'softmax', not {score!r}")
+        if not 0 < int(top) <= int(n_experts) + int(identity):
+            raise ValueError("top must lie in 1..n_experts + identity")
+        if identity and weigh != "output":
+            raise ValueError("experts that return their input are weighed on their output")
         self.d_model, self.n_experts, self.top = int(d_model), int(n_experts), int(top)
         self.expert_size, self.shared = int(expert_size), shared
         self.weigh, self.renormalise = weigh, bool(renormalise)
+        self.score, self.has_correction = score, bool(correction)
+        self.identity, self.renorm_eps = int(identity), float(renorm_eps)
+        self.n_outputs = self.n_experts + self.identity
+        self.correction = None
 
     def tensor_specs(self) -> dict:
         d, f = self.d_model, self.expert_size
-        out = {"router": TensorSpec((self.n_experts, d))}
+        out = {"router": TensorSpec((self.n_outputs, d))}
+        if self.has_correction:
+            out["correction"] = TensorSpec((self.n_outputs,), kind="vector", init="zeros")
         for i in range(self.n_experts):
             out[f"e{i}.gate"] = TensorSpec((f, d))
             out[f"e{i}.up"] = TensorSpec((f, d))
@@ -179,6 +212,8 @@ class RoutedExperts(FeedForward):
         self.runtime = runtime
         n = self.n_experts
         self.w_router = tensors["router"].float().contiguous()       # scores are float32
+        if self.has_correction:
+            self.correction = tensors["correction"].float().contiguous()
         self.w_gate_up = torch.stack([torch.cat([tensors[f"e{i}.gate"], tensors[f"e{i}.up"]], 0)
                                       for i in range(n)]).contiguous()
         self.w_down = torch.stack([tensors[f"e{i}.down"] for i in range(n)]).contiguous()
@@ -189,13 +224,13 @@ class RoutedExperts(FeedForward):
 
     def _work(self, t: int) -> dict:
         rt, n_slots = self.runtime, t * self.top
-        tiles = rt.ops.expert_max_tiles(n_slots, self.n_experts)
+        tiles = rt.ops.expert_max_tiles(n_slots, self.n_experts)   # outputs without weights get none
         i32 = torch.int32
         return {"idx": rt.buffer("route_idx", (n_slots,), i32),
                 "weight": rt.buffer("route_weight", (n_slots,), torch.float32),
                 "order": rt.buffer("route_order", (n_slots,), i32),
-                "offsets": rt.buffer("route_offsets", (self.n_experts + 1,), i32),
-                "cursor": rt.buffer("route_cursor", (self.n_experts,), i32),
+                "offsets": rt.buffer("route_offsets", (self.n_outputs + 1,), i32),
+                "cursor": rt.buffer("route_cursor", (self.n_outputs,), i32),
                 "tile_expert": rt.buffer("route_tile_expert", (tiles,), i32),
                 "tile_row0": rt.buffer("route_tile_row0", (tiles,), i32),
                 "max_tiles": tiles}
@@ -203,10 +238,11 @@ class RoutedExperts(FeedForward):
     def forward(self, h, step: StepContext):
         rt, ops = self.runtime, self.runtime.ops
         t = h.shape[0]
-        logits = rt.buffer("route_logits", (t, self.n_experts), torch.float32)
+        logits = rt.buffer("route_logits", (t, self.n_outputs), torch.float32)
         ops.linear(h, self.w_router, logits)
         work = self._work(t)
-        ops.route(logits, self.top, self.renormalise, work)
+        ops.route(logits, self.top, self.renormalise, work, softmax=self.score == "softmax",
+                  correction=self.correction, renorm_eps=self.renorm_eps, n_real=self.n_experts)
         n_slots = t * self.top
         y = rt.buffer("expert_act", (n_slots, self.expert_size), rt.act_dtype)
         per_slot = rt.buffer("expert_out", (n_slots, self.d_model), torch.float32)
@@ -218,5 +254,9 @@ class RoutedExperts(FeedForward):
             if not isinstance(shared, torch.Tensor):
                 shared = shared.float()              # a product left as its K-parts
         delta = rt.buffer("routed_delta", (t, self.d_model), rt.act_dtype)
-        ops.expert_combine(per_slot, self.top, shared, delta)
+        if self.identity:
+            ops.expert_combine(per_slot, self.top, shared, delta, work=work,
+                               n_real=self.n_experts, h=h)
+        else:
+            ops.expert_combine(per_slot, self.top, shared, delta)
         return delta

@@ -116,15 +116,16 @@ class TokenEmbedding(Part):
 
 
 class OutputHead(Part):
-    """``logits = (h @ W^T) * scale`` in float32; W is the embedding table when tied."""
+    """``logits = (h @ W^T) * scale`` in float32; W is the embedding table when tied.  With
+    ``softcap`` c > 0 the logits then become ``c * tanh(logits / c)``."""
 
     decode_capturable = prompt_capturable = True
 
     def __init__(self, vocab_size: int, d_model: int, tied_to: Optional[TokenEmbedding],
-                 tensor_name: str = "weight", scale: float = 1.0):
+                 tensor_name: str = "weight", scale: float = 1.0, softcap: float = 0.0):
         self.vocab_size, self.d_model = int(vocab_size), int(d_model)
         self.tied_to = tied_to
-        self.tensor_name, self.scale = tensor_name, float(scale)
+        self.tensor_name, self.scale, self.softcap = tensor_name, float(scale), float(softcap)
         self.weight = None
 
     def tensor_specs(self) -> dict:
@@ -143,6 +144,8 @@ class OutputHead(Part):
         rt.ops.linear(h, self.weight, logits)
         if self.scale != 1.0:
             rt.ops.scale_(logits, self.scale)
+        if self.softcap > 0.0:
+            rt.ops.softcap_(logits, self.softcap)
         return logits
 
 
