@@ -1,4 +1,4 @@
-"""``bench.py --design zededra | logulix``: prefill and decode throughput of the design's
+"""``bench.py --design zededra | logulix | zefenex``: prefill and decode throughput of the design's
 layers at sizes that resemble a real model's, beside the dense Llama-style decoder at equal
 size.
 
@@ -69,10 +69,39 @@ def logulix_config(s: dict, kind: str, layers: int, vocab: int = 32000) -> dict:
             "embedding": {"scale": 1.0}, "logit_scale": 1.0, "layers": [layer] * layers}
 
 
+def zefenex_config(s: dict, kind: str, layers: int, vocab: int = 32000) -> dict:
+    """Layers of Zefenex's latent attention (a latent of three quarters of Zededra's plus a
+    rotated key part of one quarter: the same cache bytes a token and the same attention
+    arithmetic; queries of half a head plain and half rotated; a window of 1,024, sinks, the
+    output gate) with the biased ungated feed-forward, with the routed one (softmax scores, a
+    correction, two experts that return their input, a shared expert), or with every second
+    layer reading the cache of the layer before it."""
+    g = s["kv_rank"] // 4
+    mixer = {"dim": s["dim"] - g, "heads": s["heads"], "kv_rank": s["kv_rank"] - g, "rot_dim": g,
+             "rot": {"base": 1e6, "dims": g}, "mask": {"size": 1024}, "scale": s["dim"] ** -0.5,
+             "vdim": s["dim"]}
+    dense = {"ff": s["ff"], "kind": "dense"}
+    moe = {"expert": {"ff": s["eff"]}, "kind": "moe",
+           "router": {"experts": s["experts"], "identity": 2, "top": s["top"]},
+           "shared": {"ff": s["shared"]}}
+    mlp = moe if kind == "latent_moe" else dense
+    stack = []
+    for i in range(layers):
+        m = dict(mixer)
+        if kind == "shared_cache_dense" and i % 2:
+            m["kv_from"] = i - 1
+        stack.append({"type": "latent_attention", "mixer": m, "mlp": mlp})
+    return {"architecture": "Zefenex", "vocab": vocab, "width": s["width"], "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0}, "logit_softcap": 30.0, "layers": stack}
+
+
 DESIGNS = {
     "zededra": (zededra_config, ("latent_dense", "latent_moe", "mlstm_dense")),
     "logulix": (logulix_config, ("attention_dense", "wkv_dense", "retention_dense")),
+    "zefenex": (zefenex_config, ("latent_dense", "latent_moe", "shared_cache_dense")),
 }
+# rows of another design measured beside a design's own: the closest existing layers
+BESIDE = {"zefenex": (("zededra", "latent_dense"), ("zededra", "latent_moe"))}
 
 
 def llama_config(s: dict, layers: int, vocab: int = 32000) -> dict:
@@ -90,7 +119,8 @@ _LEAVES = ("embed", "add_rmsnorm", "gather_add_rmsnorm", "add_layernorm", "resid
            "latent_norm_store", "headwise_linear", "mlstm_scan", "mlstm_finish", "route",
            "expert_glu", "expert_down", "expert_combine", "qk_conv_norm_rope_store",
            "tail_update", "token_shift_mix", "linear_scan", "scan_finish", "rotate_rows",
-           "decay_lowrank", "relu_squared", "scale_", "settle_concat")
+           "decay_lowrank", "relu_squared", "scale_", "settle_concat", "add_tanh_norm",
+           "latent_rope_prep", "sigmoid_gate", "softcap_")
 _PRODUCTS = ("linear", "linear_parts", "linear_swiglu", "linear_clamped_glu",
              "linear_relu_squared")
 
@@ -239,6 +269,9 @@ def run(args, peaks: dict, peaks_source: str) -> dict:
     for name in sizes:
         s = SIZES[name]
         rows = {"llama_dense": measure(torch, llama_config(s, layers), args.steps, args.warmup)}
+        for other, kind in BESIDE.get(design, ()):
+            rows[f"{other}_{kind}"] = measure(torch, DESIGNS[other][0](s, kind, layers), args.steps,
+                                              args.warmup)
         for kind in kinds:
             rows[f"{design}_{kind}"] = measure(torch, make_config(s, kind, layers), args.steps,
                                                args.warmup)

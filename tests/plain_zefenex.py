@@ -108,23 +108,30 @@ def plain_silu_unit(h, w, p, rnd=ident):
     return rnd(g * torch.sigmoid(g) * (h @ w[f"{p}.up"].T)) @ w[f"{p}.down"].T
 
 
-def plain_route(h, w, p, router):
+def plain_route(h, w, p, router, flip_below=0.0):
     """Softmax scores over all router outputs; the ``top`` with the largest score +
     correction (lowest index on ties); weights = the chosen scores (without the
-    correction) over their sum."""
+    correction) over their sum.  ``flip_below``: where the last chosen output leads the
+    first one left out by less than this, the other one is taken (what an engine may do
+    whose activations are rounded: the choice is a close call)."""
     s = torch.softmax(h @ w[f"{p}.router"].to(h.dtype).T, dim=-1)
     choice = s + w[f"{p}.correction"].to(h.dtype)
-    idx = torch.sort(choice, dim=-1, descending=True, stable=True).indices[:, :router["top"]]
+    order = torch.sort(choice, dim=-1, descending=True, stable=True)
+    top = router["top"]
+    idx = order.indices[:, :top].clone()
+    if flip_below and top < choice.shape[1]:
+        close = (order.values[:, top - 1] - order.values[:, top]) < flip_below
+        idx[close, top - 1] = order.indices[close, top]
     val = torch.gather(s, 1, idx)
     return idx, val / (val.sum(-1, keepdim=True) + 1e-20)
 
 
-def plain_routed_experts(h, w, p, mlp, rnd=ident):
+def plain_routed_experts(h, w, p, mlp, rnd=ident, flip_below=0.0):
     """Weighted sum of the chosen experts' outputs; the last ``identity`` router outputs
     stand for experts that return their input; a shared expert is added for every token."""
     router = mlp["router"]
     n_real = router["experts"]
-    idx, val = plain_route(h, w, p, router)
+    idx, val = plain_route(h, w, p, router, flip_below)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for j in range(router["top"]):
@@ -136,19 +143,19 @@ def plain_routed_experts(h, w, p, mlp, rnd=ident):
     return rnd(out)
 
 
-def plain_feedforward(h, w, p, mlp, rnd=ident):
+def plain_feedforward(h, w, p, mlp, rnd=ident, flip_below=0.0):
     if mlp["kind"] == "dense":
         return plain_relu2_unit(h, w, p, rnd)
-    return plain_routed_experts(h, w, p, mlp, rnd)
+    return plain_routed_experts(h, w, p, mlp, rnd, flip_below)
 
 
 # ----------------------------------------------------------------------------- model
-def plain_zefenex(w, cfg, tokens, trace=None, rnd=ident, first_position=0):
+def plain_zefenex(w, cfg, tokens, trace=None, rnd=ident, first_position=0, flip_below=0.0):
     """Logits [S, vocab] of one whole sequence; ``trace`` (a list) receives the residual
-    stream after every layer."""
+    stream after every layer; ``flip_below``: see ``plain_route``."""
     eps = cfg["norm"]["eps"]
     positions = list(range(first_position, first_position + len(tokens)))
-    x = w["embed"][torch.as_tensor(tokens)] * cfg["embedding"]["scale"]
+    x = w["embed"][torch.as_tensor(tokens)] * (cfg.get("embedding") or {}).get("scale", 1.0)
     cached = {}
     for i, L in enumerate(cfg["layers"]):
         m, p = L["mixer"], f"l{i}.mix"
@@ -160,7 +167,7 @@ def plain_zefenex(w, cfg, tokens, trace=None, rnd=ident, first_position=0):
         x = x + plain_tanh_norm(y, w, f"l{i}.norm1b") * w[f"l{i}.ls1"]
         if L.get("mlp"):
             h = rnd(plain_tanh_norm(x, w, f"l{i}.norm2"))
-            y = plain_feedforward(h, w, f"l{i}.mlp", L["mlp"], rnd)
+            y = plain_feedforward(h, w, f"l{i}.mlp", L["mlp"], rnd, flip_below)
             x = x + plain_tanh_norm(y, w, f"l{i}.norm2b") * w[f"l{i}.ls2"]
         if trace is not None:
             trace.append(x)
