@@ -126,7 +126,7 @@ class Ops:
         self._embed = _decl(core, "mls_embed", [_P, _P, _I, _P, _I, _I, _I, _F, _P, _P])
         self._add_rmsnorm = _decl(core, "mls_add_rmsnorm",
                                   [_P, _P, _I, _P, _I, _F, _P, _I, _I, _I, _P, _I, _LL, _P, _P])
-        self._gemm_f32 = _decl(core, "mls_gemm_f32", [_P, _P, _P, _I, _I, _I, _P])
+        self._gemm_f32 = _decl(core, "mls_gemm_f32", [_P, _I, _P, _P, _I, _I, _I, _P])
         self._rope_store = _decl(core, "mls_rope_store",
                                  [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
                                   _LL, _I, _P, _I, _LL, _P, _P])
@@ -281,13 +281,14 @@ class Ops:
         if m == 0:
             return
         if w.dtype == torch.float32:
-            # a matrix held in 32 bits is multiplied in true 32-bit arithmetic
-            a32 = a if a.dtype == torch.float32 else a.float()
+            # a matrix held in 32 bits is multiplied in true 32-bit arithmetic (16-bit rows
+            # of ``a`` are widened as the kernel loads them)
+            _need(a.dtype in (torch.float32, torch.bfloat16), f"linear: input dtype {a.dtype}")
             o32 = out if out.dtype == torch.float32 else torch.empty(
                 (m, n), dtype=torch.float32, device=out.device)
             self.launches += 1
-            _check(self._gemm_f32(_ptr(a32), _ptr(w), _ptr(o32), m, n, k, self._stream()),
-                   "gemm_f32")
+            _check(self._gemm_f32(_ptr(a), _code(a.dtype), _ptr(w), _ptr(o32), m, n, k,
+                                  self._stream()), "gemm_f32")
             if o32 is not out:
                 out.copy_(o32)
             return
