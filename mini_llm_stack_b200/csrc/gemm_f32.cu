@@ -102,6 +102,8 @@ gemm_f32_skinny_kernel(const void* __restrict__ A, int a_dtype, const float* __r
         __syncthreads();
         if (n0 >= N) continue;
         if (by4) {
+            // several rounds' loads of W under way at a time: the sums keep their order
+#pragma unroll 4
             for (int k = lane * 4; k < kc; k += 128) {
                 float4 a[SK_ROWS];
 #pragma unroll

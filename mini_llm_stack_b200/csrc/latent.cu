@@ -78,17 +78,42 @@ struct RowParts {
 };
 
 // Entry i of a vector of n entries whose first `dims` turn, entry j with entry j + dims/2
-// (j < dims/2), by the angle position * freq[j]; the others pass.  get(j) reads entry j.
+// (j < dims/2), by the token's angle j, whose cosine is cs[j] and sine cs[dims/2 + j]; the
+// others pass.  get(j) reads entry j.
 template <typename Get>
-__device__ __forceinline__ float rotated_entry(Get get, int i, int dims, int position,
-                                               const double* __restrict__ freq) {
+__device__ __forceinline__ float rotated_entry(Get get, int i, int dims,
+                                               const float* __restrict__ cs) {
     const int half = dims >> 1;
     if (i >= dims) return get(i);
     const int j = i < half ? i : i - half;
-    float c, s;
-    angle_cos_sin(position, freq[j], c, s);
+    const float c = cs[j], s = cs[half + j];
     const float u = get(j), v = get(j + half);
     return i < half ? u * c - v * s : v * c + u * s;
+}
+
+// Four neighbouring float32 entries of a projection row (summed over its parts), and four
+// values stored side by side in the activations' type.
+__device__ __forceinline__ float4 row_parts_at4(const RowParts& proj, int t, int col) {
+    const float* p = proj.base + (size_t)t * proj.width + col;
+    float4 v = *reinterpret_cast<const float4*>(p);
+    for (int k = 1; k < proj.n_parts; ++k) {
+        const float4 w = *reinterpret_cast<const float4*>(p + (size_t)k * proj.part_stride);
+        v.x += w.x;
+        v.y += w.y;
+        v.z += w.z;
+        v.w += w.w;
+    }
+    return v;
+}
+__device__ __forceinline__ void store4(float* dst, float4 v) {
+    *reinterpret_cast<float4*>(dst) = v;
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* dst, float4 v) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<const unsigned*>(&lo);
+    u.y = *reinterpret_cast<const unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(dst) = u;
 }
 
 // One block a token.  From the float32 projection row [q heads (e plain | g turned) ... |
@@ -97,7 +122,10 @@ __device__ __forceinline__ float rotated_entry(Get get, int i, int dims, int pos
 //   q_in[t, h * rp + r + i]              the turned part of every head, rotated (i < g);
 //                                        q_in[t, h * rp + r + g ..] = 0 up to rp
 //   pool[slot] = [unit_rms(down[:r]) * w | rotate(down[r : r + g]) | 0 ...]   (has_kv only)
-// and the rest of a page the request enters is cleared.
+// and the rest of a page the request enters is cleared.  The token's dims/2 angles are taken
+// once (the product with the position and its reduction are float64) and kept in shared
+// memory as cos | sin.  by4: every column offset and width is a multiple of four and the
+// buffers start at 16-byte addresses, so the plain parts move four entries at a time.
 template <typename T>
 __global__ void __launch_bounds__(LT_THREADS)
 latent_rope_prep_kernel(const RowParts proj, int q_col, int kv_col, int n_heads, int e, int g,
@@ -105,18 +133,32 @@ latent_rope_prep_kernel(const RowParts proj, int q_col, int kv_col, int n_heads,
                         const int* __restrict__ positions, const void* __restrict__ wkv,
                         int w_dtype, float eps, T* __restrict__ q_plain, T* __restrict__ q_in,
                         int q_in_width, int has_kv, const int* __restrict__ slot_map,
-                        T* __restrict__ pool, int block_size, int pool_slots, int* status) {
+                        T* __restrict__ pool, int block_size, int pool_slots, int by4,
+                        int* status) {
     chain_release();
+    extern __shared__ float cs[];                    // [rot_dims]: cos | sin
     const int t = blockIdx.x;
     const int pos = positions[t];
     const int slot = has_kv ? slot_map[t] : -1;
     const int tail = has_kv ? page_tail_to_clear(slot_map, t, gridDim.x, slot, block_size) : 0;
+    for (int j = threadIdx.x; j < (rot_dims >> 1); j += LT_THREADS)
+        angle_cos_sin(pos, freq[j], cs[j], cs[(rot_dims >> 1) + j]);
     chain_wait();
+    __syncthreads();
     __shared__ float scratch[33];
     const int hw = e + g;
-    for (int u = threadIdx.x; u < n_heads * e; u += LT_THREADS) {
-        const int h = u / e, i = u - h * e;
-        Elem<T>::store(q_plain + (size_t)t * n_heads * e + u, proj.at(t, q_col + h * hw + i));
+    if (by4) {
+        const int e4 = e >> 2;
+        for (int u = threadIdx.x; u < n_heads * e4; u += LT_THREADS) {
+            const int h = u / e4, i = (u - h * e4) << 2;
+            store4(q_plain + (size_t)t * n_heads * e + h * e + i,
+                   row_parts_at4(proj, t, q_col + h * hw + i));
+        }
+    } else {
+        for (int u = threadIdx.x; u < n_heads * e; u += LT_THREADS) {
+            const int h = u / e, i = u - h * e;
+            Elem<T>::store(q_plain + (size_t)t * n_heads * e + u, proj.at(t, q_col + h * hw + i));
+        }
     }
     const int turned = rp - r;                       // g rotated entries, then zeros
     for (int u = threadIdx.x; u < n_heads * turned; u += LT_THREADS) {
@@ -124,7 +166,7 @@ latent_rope_prep_kernel(const RowParts proj, int q_col, int kv_col, int n_heads,
         float v = 0.f;
         if (i < g)
             v = rotated_entry([&](int j) { return proj.at(t, q_col + h * hw + e + j); }, i,
-                              rot_dims, pos, freq);
+                              rot_dims, cs);
         Elem<T>::store(q_in + (size_t)t * q_in_width + (size_t)h * rp + r + i, v);
     }
     if (!has_kv) return;
@@ -144,18 +186,47 @@ latent_rope_prep_kernel(const RowParts proj, int q_col, int kv_col, int n_heads,
             v = proj.at(t, kv_col + c) * inv * load_as_float(wkv, c, w_dtype);
         else if (c < r + g)
             v = rotated_entry([&](int j) { return proj.at(t, kv_col + r + j); }, c - r, rot_dims,
-                              pos, freq);
+                              cs);
         Elem<T>::store(dst + c, v);
     }
     clear_page_tail<T>(tail, slot, block_size, pool_slots / block_size, 1, rp, pool, pool);
 }
 
 // o[t, c] *= sigmoid(gate[t, gate_col + c]), the gate read from a float32 projection row.
+// by4: four entries a thread where widths and offsets are multiples of four.
+__device__ __forceinline__ float4 load4(const float* src) {
+    return *reinterpret_cast<const float4*>(src);
+}
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* src) {
+    const uint2 u = *reinterpret_cast<const uint2*>(src);
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
-sigmoid_gate_kernel(T* __restrict__ o, const RowParts proj, int gate_col, int n_tokens, int n) {
+sigmoid_gate_kernel(T* __restrict__ o, const RowParts proj, int gate_col, int n_tokens, int n,
+                    int by4) {
     chain_release();
     chain_wait();
+    if (by4) {
+        const int n4 = n >> 2;
+        const size_t total = (size_t)n_tokens * n4;
+        for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+             idx += (size_t)gridDim.x * blockDim.x) {
+            const int t = (int)(idx / n4), c = (int)(idx - (size_t)t * n4) << 2;
+            const float4 z = row_parts_at4(proj, t, gate_col + c);
+            T* at = o + (size_t)t * n + c;
+            float4 v = load4(at);
+            v.x = v.x / (1.0f + expf(-z.x));
+            v.y = v.y / (1.0f + expf(-z.y));
+            v.z = v.z / (1.0f + expf(-z.z));
+            v.w = v.w / (1.0f + expf(-z.w));
+            store4(at, v);
+        }
+        return;
+    }
     const size_t total = (size_t)n_tokens * n;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
@@ -272,16 +343,21 @@ MLS_API int mls_latent_rope_prep(const float* proj, int n_parts, long long part_
         rot_dims > g || (rot_dims & 1) || (rot_dims > 0 && !freq) || (has_kv && block_size <= 0))
         return MLS_ERR_UNSUPPORTED;
     const RowParts rows{proj, n_parts, part_stride, proj_width};
+    const size_t smem = (size_t)rot_dims * sizeof(float);
+    if (smem > 40 * 1024) return MLS_ERR_UNSUPPORTED;
+    const int by4 = e % 4 == 0 && g % 4 == 0 && q_col % 4 == 0 && proj_width % 4 == 0 &&
+                    part_stride % 4 == 0 && reinterpret_cast<uintptr_t>(proj) % 16 == 0 &&
+                    reinterpret_cast<uintptr_t>(q_plain) % 16 == 0;
     if (dtype == MLS_BF16)
-        MLS_LAUNCH((latent_rope_prep_kernel<__nv_bfloat16>), dim3(n_tokens), dim3(LT_THREADS), 0,
+        MLS_LAUNCH((latent_rope_prep_kernel<__nv_bfloat16>), dim3(n_tokens), dim3(LT_THREADS), smem,
                    stream, rows, q_col, kv_col, n_heads, e, g, r, rp, rot_dims, freq, positions, wkv,
                    w_dtype, eps, (__nv_bfloat16*)q_plain, (__nv_bfloat16*)q_in, q_in_width, has_kv,
-                   slot_map, (__nv_bfloat16*)pool, block_size, (int)pool_slots, status);
+                   slot_map, (__nv_bfloat16*)pool, block_size, (int)pool_slots, by4, status);
     else
-        MLS_LAUNCH((latent_rope_prep_kernel<float>), dim3(n_tokens), dim3(LT_THREADS), 0, stream,
+        MLS_LAUNCH((latent_rope_prep_kernel<float>), dim3(n_tokens), dim3(LT_THREADS), smem, stream,
                    rows, q_col, kv_col, n_heads, e, g, r, rp, rot_dims, freq, positions, wkv, w_dtype,
                    eps, (float*)q_plain, (float*)q_in, q_in_width, has_kv, slot_map, (float*)pool,
-                   block_size, (int)pool_slots, status);
+                   block_size, (int)pool_slots, by4, status);
     return launch_status();
 }
 
@@ -291,13 +367,16 @@ MLS_API int mls_sigmoid_gate(void* o, int dtype, const float* proj, int n_parts,
     if (n_tokens <= 0 || n <= 0) return 0;
     if (n_parts < 1) return MLS_ERR_UNSUPPORTED;
     const RowParts rows{proj, n_parts, part_stride, proj_width};
-    const size_t want = ((size_t)n_tokens * n + 255) / 256;
+    const int by4 = n % 4 == 0 && gate_col % 4 == 0 && proj_width % 4 == 0 && part_stride % 4 == 0 &&
+                    reinterpret_cast<uintptr_t>(proj) % 16 == 0 &&
+                    reinterpret_cast<uintptr_t>(o) % 16 == 0;
+    const size_t want = ((size_t)n_tokens * (by4 ? n / 4 : n) + 255) / 256;
     const int blocks = (int)(want < (size_t)(8 * sm_count()) ? want : 8 * sm_count());
     if (dtype == MLS_BF16)
         MLS_LAUNCH((sigmoid_gate_kernel<__nv_bfloat16>), dim3(blocks), dim3(256), 0, stream,
-                   (__nv_bfloat16*)o, rows, gate_col, n_tokens, n);
+                   (__nv_bfloat16*)o, rows, gate_col, n_tokens, n, by4);
     else
         MLS_LAUNCH((sigmoid_gate_kernel<float>), dim3(blocks), dim3(256), 0, stream, (float*)o, rows,
-                   gate_col, n_tokens, n);
+                   gate_col, n_tokens, n, by4);
     return launch_status();
 }
