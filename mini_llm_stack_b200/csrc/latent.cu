@@ -126,6 +126,11 @@ __device__ __forceinline__ void store4(__nv_bfloat16* dst, float4 v) {
 // once (the product with the position and its reduction are float64) and kept in shared
 // memory as cos | sin.  by4: every column offset and width is a multiple of four and the
 // buffers start at 16-byte addresses, so the plain parts move four entries at a time.
+// staged: the entries that are turned or normed (every head's g and the r + g of the down
+// projection) are first brought into shared memory, all loads under way at once, and the
+// rest of the kernel reads them there; without it (a row too long for shared memory) every
+// entry is read where it is used.  kv4: the down-projected entries also move by fours.  The
+// latent norm's weight waits there too, read before the wait on the kernel ahead.
 template <typename T>
 __global__ void __launch_bounds__(LT_THREADS)
 latent_rope_prep_kernel(const RowParts proj, int q_col, int kv_col, int n_heads, int e, int g,
@@ -133,22 +138,52 @@ latent_rope_prep_kernel(const RowParts proj, int q_col, int kv_col, int n_heads,
                         const int* __restrict__ positions, const void* __restrict__ wkv,
                         int w_dtype, float eps, T* __restrict__ q_plain, T* __restrict__ q_in,
                         int q_in_width, int has_kv, const int* __restrict__ slot_map,
-                        T* __restrict__ pool, int block_size, int pool_slots, int by4,
-                        int* status) {
+                        T* __restrict__ pool, int block_size, int pool_slots, int by4, int kv4,
+                        int staged, int* status) {
     chain_release();
-    extern __shared__ float cs[];                    // [rot_dims]: cos | sin
+    extern __shared__ __align__(16) float cs[];      // [rot_dims]: cos | sin, then the staged entries
+    float* sq = cs + ((rot_dims + 3) & ~3);          // [n_heads, g]
+    float* skv = sq + n_heads * g;                   // [r + g]
+    float* swn = skv + r + g;                        // [r]: the latent norm's weight
     const int t = blockIdx.x;
     const int pos = positions[t];
     const int slot = has_kv ? slot_map[t] : -1;
     const int tail = has_kv ? page_tail_to_clear(slot_map, t, gridDim.x, slot, block_size) : 0;
     for (int j = threadIdx.x; j < (rot_dims >> 1); j += LT_THREADS)
         angle_cos_sin(pos, freq[j], cs[j], cs[(rot_dims >> 1) + j]);
+    // weights are no result of the kernel before: they may be read ahead of the wait
+    if (staged && has_kv)
+        for (int c = threadIdx.x; c < r; c += LT_THREADS) swn[c] = load_as_float(wkv, c, w_dtype);
     chain_wait();
-    __syncthreads();
-    __shared__ float scratch[33];
     const int hw = e + g;
+    if (staged) {
+        if (by4) {
+            const int g4 = g >> 2;
+#pragma unroll 4
+            for (int u = threadIdx.x; u < n_heads * g4; u += LT_THREADS) {
+                const int h = u / g4, i = (u - h * g4) << 2;
+                store4(sq + h * g + i, row_parts_at4(proj, t, q_col + h * hw + e + i));
+            }
+        } else {
+#pragma unroll 4
+            for (int u = threadIdx.x; u < n_heads * g; u += LT_THREADS) {
+                const int h = u / g, i = u - h * g;
+                sq[u] = proj.at(t, q_col + h * hw + e + i);
+            }
+        }
+        if (has_kv && kv4) {
+#pragma unroll 2
+            for (int c = threadIdx.x * 4; c < r + g; c += LT_THREADS * 4)
+                store4(skv + c, row_parts_at4(proj, t, kv_col + c));
+        } else if (has_kv) {
+#pragma unroll 4
+            for (int c = threadIdx.x; c < r + g; c += LT_THREADS) skv[c] = proj.at(t, kv_col + c);
+        }
+    }
+    __shared__ float scratch[33];
     if (by4) {
         const int e4 = e >> 2;
+#pragma unroll 2
         for (int u = threadIdx.x; u < n_heads * e4; u += LT_THREADS) {
             const int h = u / e4, i = (u - h * e4) << 2;
             store4(q_plain + (size_t)t * n_heads * e + h * e + i,
@@ -160,21 +195,24 @@ latent_rope_prep_kernel(const RowParts proj, int q_col, int kv_col, int n_heads,
             Elem<T>::store(q_plain + (size_t)t * n_heads * e + u, proj.at(t, q_col + h * hw + i));
         }
     }
+    __syncthreads();
     const int turned = rp - r;                       // g rotated entries, then zeros
     for (int u = threadIdx.x; u < n_heads * turned; u += LT_THREADS) {
         const int h = u / turned, i = u - h * turned;
         float v = 0.f;
         if (i < g)
-            v = rotated_entry([&](int j) { return proj.at(t, q_col + h * hw + e + j); }, i,
-                              rot_dims, cs);
+            v = rotated_entry(
+                [&](int j) { return staged ? sq[h * g + j] : proj.at(t, q_col + h * hw + e + j); },
+                i, rot_dims, cs);
         Elem<T>::store(q_in + (size_t)t * q_in_width + (size_t)h * rp + r + i, v);
     }
     if (!has_kv) return;
     const bool slot_ok = slot >= 0 && slot < pool_slots;
     if (!slot_ok && threadIdx.x == 0 && status) atomicOr(status, MLS_STATUS_BAD_SLOT);
+    auto down = [&](int c) { return staged ? skv[c] : proj.at(t, kv_col + c); };
     float s = 0.f;
     for (int c = threadIdx.x; c < r; c += LT_THREADS) {
-        const float v = proj.at(t, kv_col + c);
+        const float v = down(c);
         s = fmaf(v, v, s);
     }
     const float inv = 1.0f / sqrtf(block_sum(s, scratch) / (float)r + eps);
@@ -183,10 +221,9 @@ latent_rope_prep_kernel(const RowParts proj, int q_col, int kv_col, int n_heads,
     for (int c = threadIdx.x; c < rp; c += LT_THREADS) {
         float v = 0.f;
         if (c < r)
-            v = proj.at(t, kv_col + c) * inv * load_as_float(wkv, c, w_dtype);
+            v = down(c) * inv * (staged ? swn[c] : load_as_float(wkv, c, w_dtype));
         else if (c < r + g)
-            v = rotated_entry([&](int j) { return proj.at(t, kv_col + r + j); }, c - r, rot_dims,
-                              cs);
+            v = rotated_entry([&](int j) { return down(r + j); }, c - r, rot_dims, cs);
         Elem<T>::store(dst + c, v);
     }
     clear_page_tail<T>(tail, slot, block_size, pool_slots / block_size, 1, rp, pool, pool);
@@ -343,21 +380,30 @@ MLS_API int mls_latent_rope_prep(const float* proj, int n_parts, long long part_
         rot_dims > g || (rot_dims & 1) || (rot_dims > 0 && !freq) || (has_kv && block_size <= 0))
         return MLS_ERR_UNSUPPORTED;
     const RowParts rows{proj, n_parts, part_stride, proj_width};
-    const size_t smem = (size_t)rot_dims * sizeof(float);
+    // cos | sin, then (where they fit) every head's turned entries, the down projection's and
+    // the latent norm's weight
+    const size_t angles = ((size_t)rot_dims + 3) & ~(size_t)3;
+    const size_t stage = (size_t)n_heads * g + (has_kv ? (size_t)2 * r + g : 0);
+    const int staged = (angles + stage) * sizeof(float) <= 40 * 1024;
+    const size_t smem = (angles + (staged ? stage : 0)) * sizeof(float);
     if (smem > 40 * 1024) return MLS_ERR_UNSUPPORTED;
     const int by4 = e % 4 == 0 && g % 4 == 0 && q_col % 4 == 0 && proj_width % 4 == 0 &&
                     part_stride % 4 == 0 && reinterpret_cast<uintptr_t>(proj) % 16 == 0 &&
                     reinterpret_cast<uintptr_t>(q_plain) % 16 == 0;
+    const int kv4 = g % 4 == 0 && r % 4 == 0 && kv_col % 4 == 0 && (n_heads * g) % 4 == 0 &&
+                    proj_width % 4 == 0 && part_stride % 4 == 0 &&
+                    reinterpret_cast<uintptr_t>(proj) % 16 == 0;
     if (dtype == MLS_BF16)
         MLS_LAUNCH((latent_rope_prep_kernel<__nv_bfloat16>), dim3(n_tokens), dim3(LT_THREADS), smem,
                    stream, rows, q_col, kv_col, n_heads, e, g, r, rp, rot_dims, freq, positions, wkv,
                    w_dtype, eps, (__nv_bfloat16*)q_plain, (__nv_bfloat16*)q_in, q_in_width, has_kv,
-                   slot_map, (__nv_bfloat16*)pool, block_size, (int)pool_slots, by4, status);
+                   slot_map, (__nv_bfloat16*)pool, block_size, (int)pool_slots, by4, kv4, staged,
+                   status);
     else
         MLS_LAUNCH((latent_rope_prep_kernel<float>), dim3(n_tokens), dim3(LT_THREADS), smem, stream,
                    rows, q_col, kv_col, n_heads, e, g, r, rp, rot_dims, freq, positions, wkv, w_dtype,
                    eps, (float*)q_plain, (float*)q_in, q_in_width, has_kv, slot_map, (float*)pool,
-                   block_size, (int)pool_slots, by4, status);
+                   block_size, (int)pool_slots, by4, kv4, staged, status);
     return launch_status();
 }
 

@@ -252,6 +252,12 @@ ONE_LAYER = {
                                       width=96),
     "attention_pool_272": Z.one_layer(Z.latent(2, 16, 16, 8, 256, 0.2, window=25, base=100.0),
                                       width=48),
+    "attention_pool_240": Z.one_layer(Z.latent(3, 24, 32, 16, 200, 0.1, window=37, base=1e4),
+                                      width=56),
+    # 44 heads of 240 turned entries: more than the preparation kernel holds in shared memory,
+    # so it reads every entry where it is used
+    "attention_long_rows": Z.one_layer(Z.latent(44, 4, 240, 4, 16, 0.06, window=30, base=1e5),
+                                       width=32),
     "dense": Z.one_layer(Z.latent(1, 8, 2, 8, 6, 0.5, base=10.0), Z.dense(56)),
     "dense_wide": Z.one_layer(Z.latent(1, 8, 8, 8, 8, 0.5, base=10.0), Z.dense(200), width=64),
     "moe_identity_shared": Z.one_layer(Z.latent(1, 8, 2, 8, 6, 0.5, base=10.0),
