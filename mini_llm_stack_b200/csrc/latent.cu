@@ -63,7 +63,19 @@ latent_norm_store_kernel(const float* __restrict__ down, int rq, int r, int rp,
 }
 
 
-// Values of a projection's row that may still lie in the parts of a cut along K.
+// Values of a projection's row that may still lie in the parts of a cut along K.  The parts'
+// loads go out B at a time (a lone block of a decode step would otherwise wait for one part
+// after the other); the additions keep the parts' order.
+template <int B, typename V, typename Ld, typename Add>
+__device__ __forceinline__ void add_parts(V& v, int& k, int n, Ld ld, Add add) {
+    for (; k + B <= n; k += B) {
+        V w[B];
+#pragma unroll
+        for (int i = 0; i < B; ++i) w[i] = ld(k + i);
+#pragma unroll
+        for (int i = 0; i < B; ++i) add(v, w[i]);
+    }
+}
 struct RowParts {
     const float* base;             // [n_parts][T, width]
     int n_parts;
@@ -71,8 +83,14 @@ struct RowParts {
     int width;
     __device__ __forceinline__ float at(int t, int col) const {
         const float* p = base + (size_t)t * width + col;
+        if (n_parts == 1) return *p;
         float v = 0.f;
-        for (int k = 0; k < n_parts; ++k) v += p[(size_t)k * part_stride];
+        int k = 0;
+        auto ld = [&](int i) { return p[(size_t)i * part_stride]; };
+        auto add = [](float& a, float b) { a += b; };
+        add_parts<8>(v, k, n_parts, ld, add);
+        add_parts<4>(v, k, n_parts, ld, add);
+        add_parts<1>(v, k, n_parts, ld, add);
         return v;
     }
 };
@@ -95,14 +113,21 @@ __device__ __forceinline__ float rotated_entry(Get get, int i, int dims,
 // values stored side by side in the activations' type.
 __device__ __forceinline__ float4 row_parts_at4(const RowParts& proj, int t, int col) {
     const float* p = proj.base + (size_t)t * proj.width + col;
-    float4 v = *reinterpret_cast<const float4*>(p);
-    for (int k = 1; k < proj.n_parts; ++k) {
-        const float4 w = *reinterpret_cast<const float4*>(p + (size_t)k * proj.part_stride);
-        v.x += w.x;
-        v.y += w.y;
-        v.z += w.z;
-        v.w += w.w;
-    }
+    if (proj.n_parts == 1) return *reinterpret_cast<const float4*>(p);
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    int k = 0;
+    auto ld = [&](int i) {
+        return *reinterpret_cast<const float4*>(p + (size_t)i * proj.part_stride);
+    };
+    auto add = [](float4& a, const float4& b) {
+        a.x += b.x;
+        a.y += b.y;
+        a.z += b.z;
+        a.w += b.w;
+    };
+    add_parts<8>(v, k, proj.n_parts, ld, add);
+    add_parts<4>(v, k, proj.n_parts, ld, add);
+    add_parts<1>(v, k, proj.n_parts, ld, add);
     return v;
 }
 __device__ __forceinline__ void store4(float* dst, float4 v) {

@@ -107,7 +107,19 @@ __global__ void __launch_bounds__(256) add_tanh_norm_kernel4(const TanhNormArgs 
             if (a.delta_dtype == MLS_BF16) {
                 load4(a.delta, at, MLS_BF16, y);
             } else {
-                for (int k = 0; k < a.n_parts; ++k) {
+                // four parts' loads under way at a time; the additions keep the parts' order
+                int k = 0;
+                for (; k + 4 <= a.n_parts; k += 4) {
+                    float p[4][4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        load4(a.delta, (size_t)(k + j) * a.part_stride + at, MLS_F32, p[j]);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) y[e] += p[j][e];
+                }
+                for (; k < a.n_parts; ++k) {
                     float p[4];
                     load4(a.delta, (size_t)k * a.part_stride + at, MLS_F32, p);
 #pragma unroll
