@@ -123,10 +123,8 @@ def _module_key(name: str, defines: dict) -> tuple:
 def library_path(name: str, defines: dict | None = None) -> Path:
     """Where the module's library is, or would be built."""
     stem, _ = _module_key(name, defines or {})
-    for d in (CSRC / "_build",
-              Path(tempfile.gettempdir()) / f"mini_llm_stack_b200_build_{os.getuid()}"):
-        if (d / f"{stem}.so").is_file():
-            return d / f"{stem}.so"
+    # the folder that can be written decides: a copy under tmp from a time when the tree
+    # could not be written does not keep the library out of the tree
     return _build_dir() / f"{stem}.so"
 
 
