@@ -13,7 +13,8 @@ Here the model's cache slots (one per layer call that owns a cache) are sorted
 into groups by what they need.  Slots with the same ``PagedKV`` spec share one
 page pool and one block table per request (a page id means the same page in
 every member of the group, as one table serves all layers in the reference);
-a group with a window gives pages back as soon as the window has passed them.
+a group with a window gives pages back as soon as the window has passed them (but
+never the pages of the sequence's first ``keep_first`` tokens, if the spec names some).
 Slots with a ``FixedState`` spec share the request's state slot.  A slot whose spec is
 ``PagedWithState`` is a member of a paged group and of a fixed group at once.
 
@@ -165,6 +166,11 @@ class CacheManager:
     def live(self) -> list:
         return list(self._records)
 
+    def _keep_pages(self, g: PagedGroup) -> int:
+        """Pages at a sequence's start that a window group never gives back."""
+        keep = getattr(g.spec, "keep_first", 0) or 0
+        return self.pages_for(keep) if g.spec.window is not None else 0
+
     def _most_pages(self, g: PagedGroup, n_tokens: int, portion: int | None) -> int:
         """Most pages of group ``g`` a request of ``n_tokens`` holds at one time
         when it is fed at most ``portion`` tokens a step (all at once if None)."""
@@ -173,7 +179,7 @@ class CacheManager:
         if w is not None and portion is not None:
             # keys older than the window are given back after every step; one
             # page more because the live span need not start at a page's edge
-            need = min(need, self.pages_for(w - 1 + portion) + 1)
+            need = min(need, self.pages_for(w - 1 + portion) + 1 + self._keep_pages(g))
         return need
 
     def can_hold(self, n_tokens: int, portion: int | None = None) -> bool:
@@ -251,7 +257,8 @@ class CacheManager:
             # j > position - w, so every key < length - w + 1 is never read again
             dead = max(0, rec.length - w + 1) // self.block_size
             dead = min(dead, rec.n_pages[g.gid])
-            first = rec.released[g.gid]
+            # (the pages given back are those from the kept ones up to ``released``)
+            first = max(rec.released[g.gid], self._keep_pages(g))
             if dead > first:
                 pages = [int(p) for p in g.table[rec.row, first:dead]]
                 g.pool.give(list(reversed(pages)), owner)
@@ -294,8 +301,8 @@ class CacheManager:
         """Give back everything ``owner`` holds (serve/kv_cache.py:75-77)."""
         rec = self._records.pop(owner)
         for g in self.paged:
-            first, n = rec.released[g.gid], rec.n_pages[g.gid]
-            pages = [int(p) for p in g.table[rec.row, first:n]]
+            n = rec.n_pages[g.gid]
+            pages = [int(p) for p in g.table[rec.row, :n] if p >= 0]
             g.pool.give(list(reversed(pages)), owner)
             g.table[rec.row, :n] = -1
         self.slots.release(rec.row, owner)
@@ -313,7 +320,7 @@ class CacheManager:
             held = 0
             for owner, rec in self._records.items():
                 for i, p in enumerate(g.table[rec.row, :rec.n_pages[g.gid]]):
-                    if i < rec.released[g.gid]:
+                    if self._keep_pages(g) <= i < rec.released[g.gid]:
                         if p != -1:
                             raise CacheError("a released table entry still names a page")
                         continue

@@ -86,4 +86,4 @@ def _ensure_builtin() -> None:
     global _builtin_done
     if not _builtin_done:
         _builtin_done = True
-        from ..parts import llama_dense, logulix, zededra, zefenex  # noqa: F401  (they register themselves)
+        from ..parts import llama_dense, logulix, movazen, zededra, zefenex  # noqa: F401  (they register themselves)

@@ -8,7 +8,10 @@
 // float32, rounded once.  q head h reads kv head h / G.  With a window w, keys
 // j <= p - w are hidden too.  With a cap c > 0 the score becomes c * tanh(S / c) before
 // the softmax.  With sinks (one learned number per q head) the softmax's denominator also
-// holds exp(sink_h): a term without key or value, not scaled and not capped.  The paged walk follows the reference's decode
+// holds exp(sink_h): a term without key or value, not scaled and not capped.  With slopes
+// (one number per q head) the score loses slope_h * (p - j), the distance to the key, before
+// the cap.  With keep_first > 0 a window does not hide the sequence's first keep_first keys.
+// A row of `out` may be wider than the heads (out_stride elements a token).  The paged walk follows the reference's decode
 // kernel (kernels/paged_attention.py:34-88): page = table[r, j / block],
 // offset = j % block, online softmax over chunks of keys.
 //
@@ -65,7 +68,8 @@ attention_simt_kernel(const T* __restrict__ qkv, T* __restrict__ out,
                       const int* __restrict__ positions, const int* __restrict__ req_of_token,
                       int n_tokens, int n_heads, int n_kv, int hd, int block_size, float scale,
                       int window, float softcap, long long n_pages,
-                      const float* __restrict__ sink) {
+                      const float* __restrict__ sink, const float* __restrict__ slopes,
+                      int keep_first, long long out_stride) {
     chain_release();
     chain_wait();
     __shared__ float q_s[WARPS][MAX_HD];
@@ -91,14 +95,21 @@ attention_simt_kernel(const T* __restrict__ qkv, T* __restrict__ out,
 #pragma unroll
     for (int i = 0; i < MAX_HD / 32; ++i) acc[i] = 0.f;
 
-    for (int j0 = (j_lo / 32) * 32; j0 <= p; j0 += 32) {
+    const int keep = j_lo > 0 ? min(keep_first, j_lo) : 0;   // kept keys the window would hide
+    const float slope = slopes ? slopes[h] : 0.f;
+    for (int j0 = keep > 0 ? 0 : (j_lo / 32) * 32; j0 <= p; j0 += 32) {
+        if (j0 >= keep && j0 + 32 <= j_lo) {          // past the kept keys: on to the window
+            j0 = (j_lo / 32) * 32 - 32;
+            continue;
+        }
         const int j = j0 + lane;
-        const bool valid = j >= j_lo && j <= p;
+        const bool valid = (j >= j_lo || j < keep) && j <= p;
         float s = -INFINITY;
         if (valid) {
             const int page = table[j / block_size];
             const T* kr = k_pool + (((size_t)kvh * n_pages + page) * block_size + j % block_size) * hd;
             s = dot_row(q_s[warp], kr, hd) * scale;
+            if (slopes) s -= slope * (float)(p - j);
             if (softcap > 0.f) s = softcap * tanhf(s / softcap);
         }
         const float m_new = fmaxf(m, warp_max(s));
@@ -109,7 +120,7 @@ attention_simt_kernel(const T* __restrict__ qkv, T* __restrict__ out,
         for (int i = 0; i < MAX_HD / 32; ++i) acc[i] *= corr;
         for (int jj = 0; jj < 32; ++jj) {
             const int key = j0 + jj;
-            if (key < j_lo || key > p) continue;        // uniform across the warp
+            if ((key < j_lo && key >= keep) || key > p) continue;        // uniform across the warp
             const float pk = __shfl_sync(0xffffffffu, pj, jj);
             const int page = table[key / block_size];
             const T* vr = v_pool + (((size_t)kvh * n_pages + page) * block_size + key % block_size) * hd;
@@ -121,7 +132,7 @@ attention_simt_kernel(const T* __restrict__ qkv, T* __restrict__ out,
         }
         m = m_new;
     }
-    T* op = out + (size_t)t * n_heads * hd + (size_t)h * hd;
+    T* op = out + (size_t)t * out_stride + (size_t)h * hd;
     if (sink) l += expf(sink[h] - m);         // every token sees itself: m is a number
     const float inv = 1.0f / l;
 #pragma unroll
@@ -137,9 +148,11 @@ MLS_API int mls_attention_simt(const void* qkv, void* out, int dtype, const void
                                const int* positions, const int* req_of_token, int n_tokens,
                                int n_heads, int n_kv, int hd, int block_size, float scale,
                                int window, float softcap, long long n_pages, const float* sink,
+                               const float* slopes, int keep_first, long long out_stride,
                                cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hd > MAX_HD || hd <= 0 || n_heads % n_kv) return MLS_ERR_UNSUPPORTED;
+    if (out_stride <= 0) out_stride = (long long)n_heads * hd;
     const long long units = (long long)n_tokens * n_heads;
     const int blocks = (int)((units + WARPS - 1) / WARPS);
     if (dtype == MLS_BF16)
@@ -147,11 +160,11 @@ MLS_API int mls_attention_simt(const void* qkv, void* out, int dtype, const void
                    stream, (const __nv_bfloat16*)qkv, (__nv_bfloat16*)out,
                    (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, block_table,
                    max_blocks, positions, req_of_token, n_tokens, n_heads, n_kv, hd, block_size,
-                   scale, window, softcap, n_pages, sink);
+                   scale, window, softcap, n_pages, sink, slopes, keep_first, out_stride);
     else
         MLS_LAUNCH((attention_simt_kernel<float>), dim3(blocks), dim3(WARPS * 32), 0, stream,
                    (const float*)qkv, (float*)out, (const float*)k_pool, (const float*)v_pool,
                    block_table, max_blocks, positions, req_of_token, n_tokens, n_heads, n_kv, hd,
-                   block_size, scale, window, softcap, n_pages, sink);
+                   block_size, scale, window, softcap, n_pages, sink, slopes, keep_first, out_stride);
     return launch_status();
 }

@@ -3,17 +3,22 @@
 // mls_route_topk: scores s = sigmoid(z), or softmax(z) over all outputs, of float32 router
 //   logits z [T, E]; for every token the `top` largest scores (plus a per-output correction
 //   that enters the choice only; the lowest index wins a tie) with the scores themselves as
-//   weights (optionally divided by their sum + renorm_eps).  A (token, choice) pair is a
-//   "slot": slot = t * top + j.  Outputs n_real .. E-1 stand for experts without weights that
+//   weights (optionally divided by their sum + renorm_eps).  With n_groups > 1 the outputs form
+//   n_groups equal groups of neighbours; a group's score is the sum of its two largest choice
+//   scores, and only outputs of the keep_groups best groups (lowest index on a tie) can be
+//   chosen.  A (token, choice) pair is a "slot": slot = t * top + j.  Outputs n_real .. E-1 stand for experts without weights that
 //   return their input: they get no tiles, and mls_expert_combine adds weight * h for them.
 // mls_route_sort: slots ordered by expert: order[p] = slot, offsets[E + 1], and the list
 //   of row tiles (tile_expert, tile_row0) the products below walk.  One CTA.
-// mls_expert_glu: y[p, :] = silu(Wg[e] a) * (Wu[e] a) with a = weight[slot] * h[token]
+// mls_expert_glu: y[p, :] = unit(Wg[e] a, Wu[e] a) with unit(g, u) = silu(g) * u or, with a
+//   limit > 0, g' * sigmoid(alpha g') * (u' + 1), g' = min(g, limit), u' = clamp(u, +-limit);
+//   a = weight[slot] * h[token]
 //   (input scaling: the weight multiplies what enters the expert) or a = h[token]
 //   (output scaling, applied by the down product instead).
 // mls_expert_down: per_slot[slot, :] = Wd[e] y[p, :] (times the weight with output
 //   scaling), float32.
-// mls_expert_combine: delta[t] = sum_j per_slot[t * top + j] + shared[t], j ascending.
+// mls_expert_combine: delta[t] = sum_j per_slot[t * top + j] + shared[t], j ascending; with a
+//   gate (float32, one number a token) the shared addend is multiplied by sigmoid(gate[t]).
 //
 // The products run with float32 accumulation over k ascending (bfloat16 rows of whole
 // 16-byte pieces on the tensor cores, everything else on CUDA cores), one row
@@ -25,17 +30,21 @@
 namespace {
 constexpr int BM = 32, BN = 64, BK = 32, TM = 2, TN = 4;   // 256 threads
 
-__global__ void route_topk_kernel(const float* __restrict__ logits, int n_tokens, int n_experts,
-                                  int top, int renorm, int softmax,
+constexpr int MAX_GROUPS = 256;
+
+__global__ void route_topk_kernel(const float* __restrict__ logits, int logit_stride, int n_tokens,
+                                  int n_experts, int top, int renorm, int softmax,
                                   const float* __restrict__ correction, float renorm_eps,
+                                  int n_groups, int keep_groups,
                                   int* __restrict__ idx, float* __restrict__ weight) {
     chain_release();
     chain_wait();
     // one warp a token
+    __shared__ float group_score[4][MAX_GROUPS];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * (blockDim.x >> 5) + warp;
     if (t >= n_tokens) return;
-    const float* z = logits + (size_t)t * n_experts;
+    const float* z = logits + (size_t)t * logit_stride;
     // softmax over all outputs: the largest logit and the sum of exponentials, both in the
     // order of the lanes' strides, so a token's scores do not depend on its batch
     float z_max = 0.f, inv_sum = 1.f;
@@ -47,12 +56,37 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, int n_tokens
         for (int e = lane; e < n_experts; e += 32) sum += expf(z[e] - z_max);
         inv_sum = 1.0f / warp_sum(sum);
     }
+    const int group_size = n_groups > 1 ? n_experts / n_groups : n_experts;
+    if (n_groups > 1) {
+        // a group's score: the sum of its two largest choice scores (one, if it has one member)
+        for (int g = lane; g < n_groups; g += 32) {
+            float a = -INFINITY, b = -INFINITY;
+            for (int e = g * group_size; e < (g + 1) * group_size; ++e) {
+                const float s = softmax ? expf(z[e] - z_max) * inv_sum : 1.0f / (1.0f + expf(-z[e]));
+                const float c = correction ? s + correction[e] : s;
+                if (c > a) { b = a; a = c; } else if (c > b) { b = c; }
+            }
+            group_score[warp][g] = group_size > 1 ? a + b : a;
+        }
+        __syncwarp();
+    }
     float total = 0.f;
     for (int j = 0; j < top; ++j) {
         float best = -INFINITY, best_s = 0.f;
         int arg = 0x7fffffff;
         for (int e = lane; e < n_experts; e += 32) {
             bool taken = false;
+            if (n_groups > 1) {
+                // the group's rank: how many groups come before it
+                const int g = e / group_size;
+                const float mine = group_score[warp][g];
+                int before = 0;
+                for (int o = 0; o < n_groups; ++o) {
+                    const float other = group_score[warp][o];
+                    before += (other > mine || (other == mine && o < g)) ? 1 : 0;
+                }
+                taken = before >= keep_groups;
+            }
             for (int p = 0; p < j; ++p) taken |= idx[(size_t)t * top + p] == e;
             const float s = softmax ? expf(z[e] - z_max) * inv_sum : 1.0f / (1.0f + expf(-z[e]));
             const float c = correction ? s + correction[e] : s;      // the choice's score
@@ -177,6 +211,16 @@ __device__ __forceinline__ void fill_tile(float (*tile)[ROWS + PAD], int k0, int
     }
 }
 
+// The gated unit on the two products' float32 sums.
+__device__ __forceinline__ float gated_unit(float g, float u, float alpha, float limit) {
+    if (limit > 0.f) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return (g / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+    }
+    return (g / (1.0f + expf(-g))) * u;
+}
+
 // GLU: A row = h[slot / top] (* weight[slot] if scale), W = [gate rows | up rows] of
 // expert e ([2F, K]), out y[p, n] = silu(gate) * up in T.
 // !GLU: A row = y[p], W = Wd[e] ([N, K]), out per_slot[slot, n] float32 (* weight[slot]
@@ -186,7 +230,8 @@ __global__ void __launch_bounds__(256)
 expert_gemm_kernel(const T* __restrict__ A, const T* __restrict__ W, void* __restrict__ out,
                    const int* __restrict__ order, const int* __restrict__ offsets,
                    const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
-                   const float* __restrict__ weight, int top, int scale, int N, int K) {
+                   const float* __restrict__ weight, int top, int scale, int N, int K,
+                   float alpha, float limit) {
     chain_release();
     chain_wait();
     const int e = tile_expert[blockIdx.y];
@@ -260,9 +305,8 @@ expert_gemm_kernel(const T* __restrict__ A, const T* __restrict__ W, void* __res
             const int n = n0 + tx + 16 * j;
             if (n >= N) continue;
             if (GLU) {
-                const float g = acc[i][j];
                 Elem<T>::store((T*)out + (size_t)(p0 + r) * N + n,
-                               (g / (1.0f + expf(-g))) * acu[i][j]);
+                               gated_unit(acc[i][j], acu[i][j], alpha, limit));
             } else {
                 ((float*)out)[(size_t)slot * N + n] = scale ? acc[i][j] * weight[slot] : acc[i][j];
             }
@@ -298,7 +342,8 @@ expert_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __re
                   void* __restrict__ out, const int* __restrict__ order,
                   const int* __restrict__ offsets, const int* __restrict__ tile_expert,
                   const int* __restrict__ tile_row0, int max_tiles,
-                  const float* __restrict__ weight, int top, int scale, int N, int K) {
+                  const float* __restrict__ weight, int top, int scale, int N, int K,
+                  float alpha, float limit) {
     chain_release();
     chain_wait();
     constexpr int MROWS = RT * BM;
@@ -426,7 +471,7 @@ expert_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __re
                         const float v = acc[mf][nf][2 * half + x];
                         if (GLU)
                             ((__nv_bfloat16*)out)[(size_t)(p0 + r) * N + n] = __float2bfloat16_rn(
-                                (v / (1.0f + expf(-v))) * acu[mf][nf][2 * half + x]);
+                                gated_unit(v, acu[mf][nf][2 * half + x], alpha, limit));
                         else
                             ((float*)out)[(size_t)slot * N + n] = scale ? v * weight[slot] : v;
                     }
@@ -445,6 +490,7 @@ __global__ void expert_combine_kernel(const float* __restrict__ per_slot, int to
                                       const void* __restrict__ shared, int shared_dtype,
                                       const int* __restrict__ idx, const float* __restrict__ weight,
                                       int n_real, const T* __restrict__ h,
+                                      const float* __restrict__ gate, int gate_stride,
                                       T* __restrict__ delta, size_t n, int d) {
     chain_release();
     chain_wait();
@@ -459,7 +505,10 @@ __global__ void expert_combine_kernel(const float* __restrict__ per_slot, int to
             else
                 s += per_slot[(t * top + j) * d + c];
         }
-        if (shared) s += load_as_float(shared, i, shared_dtype);
+        if (shared) {
+            const float v = load_as_float(shared, i, shared_dtype);
+            s += gate ? v / (1.0f + expf(-gate[t * gate_stride])) : v;
+        }
         Elem<T>::store(delta + i, s);
     }
 }
@@ -467,13 +516,18 @@ __global__ void expert_combine_kernel(const float* __restrict__ per_slot, int to
 
 MLS_API int mls_expert_tile_rows() { return BM; }
 
-MLS_API int mls_route_topk(const float* logits, int n_tokens, int n_experts, int top, int renorm,
-                           int softmax, const float* correction, float renorm_eps, int* idx,
+MLS_API int mls_route_topk(const float* logits, int logit_stride, int n_tokens, int n_experts,
+                           int top, int renorm, int softmax, const float* correction,
+                           float renorm_eps, int n_groups, int keep_groups, int* idx,
                            float* weight, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (top <= 0 || top > n_experts) return MLS_ERR_UNSUPPORTED;
+    if (n_groups > 1 && (n_groups > MAX_GROUPS || n_experts % n_groups || keep_groups < 1 ||
+                         keep_groups > n_groups || top > keep_groups * (n_experts / n_groups)))
+        return MLS_ERR_UNSUPPORTED;
     MLS_LAUNCH((route_topk_kernel), dim3((n_tokens + 3) / 4), dim3(128), 0, stream, logits,
-               n_tokens, n_experts, top, renorm, softmax, correction, renorm_eps, idx, weight);
+               logit_stride, n_tokens, n_experts, top, renorm, softmax, correction, renorm_eps,
+               n_groups, keep_groups, idx, weight);
     return launch_status();
 }
 
@@ -490,25 +544,26 @@ MLS_API int mls_route_sort(const int* idx, int n_slots, int n_experts, int n_rea
 MLS_API int mls_expert_glu(const void* h, const void* w_gate_up, void* y, int dtype,
                            const int* order, const int* offsets, const int* tile_expert,
                            const int* tile_row0, int max_tiles, const float* weight, int top,
-                           int scale_in, int F, int K, int many_rows, cudaStream_t stream) {
+                           int scale_in, int F, int K, int many_rows, float alpha, float limit,
+                           cudaStream_t stream) {
     if (max_tiles <= 0) return 0;
     dim3 grid((F + BN - 1) / BN, max_tiles);
     if (takes_mma(dtype, h, w_gate_up, K) && many_rows)
         MLS_LAUNCH((expert_mma_kernel<true, 4>), dim3(grid.x, (max_tiles + 3) / 4), dim3(256), 0,
                    stream, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w_gate_up, y, order, offsets,
-                   tile_expert, tile_row0, max_tiles, weight, top, scale_in, F, K);
+                   tile_expert, tile_row0, max_tiles, weight, top, scale_in, F, K, alpha, limit);
     else if (takes_mma(dtype, h, w_gate_up, K))
         MLS_LAUNCH((expert_mma_kernel<true, 1>), dim3(grid), dim3(256), 0, stream,
                    (const __nv_bfloat16*)h, (const __nv_bfloat16*)w_gate_up, y, order, offsets,
-                   tile_expert, tile_row0, max_tiles, weight, top, scale_in, F, K);
+                   tile_expert, tile_row0, max_tiles, weight, top, scale_in, F, K, alpha, limit);
     else if (dtype == MLS_BF16)
         MLS_LAUNCH((expert_gemm_kernel<__nv_bfloat16, true>), dim3(grid), dim3(256), 0, stream,
                    (const __nv_bfloat16*)h, (const __nv_bfloat16*)w_gate_up, y, order, offsets,
-                   tile_expert, tile_row0, weight, top, scale_in, F, K);
+                   tile_expert, tile_row0, weight, top, scale_in, F, K, alpha, limit);
     else
         MLS_LAUNCH((expert_gemm_kernel<float, true>), dim3(grid), dim3(256), 0, stream,
                    (const float*)h, (const float*)w_gate_up, y, order, offsets, tile_expert,
-                   tile_row0, weight, top, scale_in, F, K);
+                   tile_row0, weight, top, scale_in, F, K, alpha, limit);
     return launch_status();
 }
 
@@ -521,26 +576,26 @@ MLS_API int mls_expert_down(const void* y, const void* w_down, float* per_slot, 
     if (takes_mma(dtype, y, w_down, F) && many_rows)
         MLS_LAUNCH((expert_mma_kernel<false, 4>), dim3(grid.x, (max_tiles + 3) / 4), dim3(256), 0,
                    stream, (const __nv_bfloat16*)y, (const __nv_bfloat16*)w_down, (void*)per_slot,
-                   order, offsets, tile_expert, tile_row0, max_tiles, weight, top, scale_out, D, F);
+                   order, offsets, tile_expert, tile_row0, max_tiles, weight, top, scale_out, D, F, 0.f, 0.f);
     else if (takes_mma(dtype, y, w_down, F))
         MLS_LAUNCH((expert_mma_kernel<false, 1>), dim3(grid), dim3(256), 0, stream,
                    (const __nv_bfloat16*)y, (const __nv_bfloat16*)w_down, (void*)per_slot, order,
-                   offsets, tile_expert, tile_row0, max_tiles, weight, top, scale_out, D, F);
+                   offsets, tile_expert, tile_row0, max_tiles, weight, top, scale_out, D, F, 0.f, 0.f);
     else if (dtype == MLS_BF16)
         MLS_LAUNCH((expert_gemm_kernel<__nv_bfloat16, false>), dim3(grid), dim3(256), 0, stream,
                    (const __nv_bfloat16*)y, (const __nv_bfloat16*)w_down, (void*)per_slot, order,
-                   offsets, tile_expert, tile_row0, weight, top, scale_out, D, F);
+                   offsets, tile_expert, tile_row0, weight, top, scale_out, D, F, 0.f, 0.f);
     else
         MLS_LAUNCH((expert_gemm_kernel<float, false>), dim3(grid), dim3(256), 0, stream,
                    (const float*)y, (const float*)w_down, (void*)per_slot, order, offsets,
-                   tile_expert, tile_row0, weight, top, scale_out, D, F);
+                   tile_expert, tile_row0, weight, top, scale_out, D, F, 0.f, 0.f);
     return launch_status();
 }
 
 MLS_API int mls_expert_combine(const float* per_slot, int top, const void* shared,
                                int shared_dtype, const int* idx, const float* weight, int n_real,
-                               const void* h, void* delta, int dtype, int n_tokens, int d,
-                               cudaStream_t stream) {
+                               const void* h, const float* gate, int gate_stride, void* delta,
+                               int dtype, int n_tokens, int d, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     const size_t n = (size_t)n_tokens * d;
     const size_t want = (n + 255) / 256;
@@ -548,10 +603,10 @@ MLS_API int mls_expert_combine(const float* per_slot, int top, const void* share
     if (dtype == MLS_BF16)
         MLS_LAUNCH((expert_combine_kernel<__nv_bfloat16>), dim3(blocks), dim3(256), 0, stream,
                    per_slot, top, shared, shared_dtype, idx, weight, n_real, (const __nv_bfloat16*)h,
-                   (__nv_bfloat16*)delta, n, d);
+                   gate, gate_stride, (__nv_bfloat16*)delta, n, d);
     else
         MLS_LAUNCH((expert_combine_kernel<float>), dim3(blocks), dim3(256), 0, stream, per_slot,
-                   top, shared, shared_dtype, idx, weight, n_real, (const float*)h, (float*)delta,
-                   n, d);
+                   top, shared, shared_dtype, idx, weight, n_real, (const float*)h, gate, gate_stride,
+                   (float*)delta, n, d);
     return launch_status();
 }

@@ -18,13 +18,16 @@
 // them side by side where only the state's own update has to wait for the token before.
 //
 //   mls_scan_finish      o / rms(o) per head (eps inside the root) * weight * silu(gate)
+//   mls_scan_finish_row  o / rms(o) over a token's whole row of heads * weight * sigmoid(gate)
+//                        * a constant, into rows that may be wider than the heads
 //   mls_rotate_rows      rotation of the first `dims` entries of every head of q and k,
 //                        entry i paired with i + dims/2, k then times a constant; float32 out
 //   mls_decay_lowrank    w = exp(-exp(W2 tanh(lo) + w0)) from the low-rank pre-activation
 //                        (W2 handed over transposed)
 //
 // State, decays, exponentials, angles' cosines and sines, norms and sums are float32 (the
-// angles themselves float64: position * frequency); a, k, v come from the projections.
+// angles themselves float64: position * frequency); a, k, v come from the projections, with
+// `act` = 1 through silu (z * sigmoid(z), float32) as they are loaded.
 #include "common.cuh"
 
 namespace {
@@ -45,6 +48,11 @@ __device__ __forceinline__ float4 load4(const void* base, int dtype, size_t i) {
     return *reinterpret_cast<const float4*>((const float*)base + i);
 }
 
+__device__ __forceinline__ float silu1(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float4 silu4(float4 v) {
+    return make_float4(silu1(v.x), silu1(v.y), silu1(v.z), silu1(v.w));
+}
+
 // (Four CTAs an SM up to 16 rows a thread: 592 places, so that the 512 CTAs of 32 heads with
 // 256 value columns are one round and not two.)
 template <int RPT, bool TOK_DECAY>
@@ -57,7 +65,7 @@ linear_scan_kernel(const void* __restrict__ a_src, int a_dtype, int a_row, int a
                    const void* __restrict__ bonus, int bonus_dtype, int read_first,
                    const int* __restrict__ cu_q, const int* __restrict__ state_slot,
                    float* __restrict__ state, long long state_stride,
-                   int n_heads, int e, int f, int tokens_a_pass, float* __restrict__ out) {
+                   int n_heads, int e, int f, int tokens_a_pass, float* __restrict__ out, int act) {
     chain_release();
     chain_wait();
     const int r = blockIdx.z, head = blockIdx.y, col0 = blockIdx.x * LS_COLS;
@@ -104,6 +112,10 @@ linear_scan_kernel(const void* __restrict__ a_src, int a_dtype, int a_row, int a
                         const size_t t = (size_t)(t0 + b0 + tt);
                         av[j] = load4(a_src, a_dtype, t * a_row + a_off + head * e + i);
                         kv[j] = load4(k_src, k_dtype, t * k_row + k_off + head * e + i);
+                        if (act) {
+                            av[j] = silu4(av[j]);
+                            kv[j] = silu4(kv[j]);
+                        }
                         wv[j] = TOK_DECAY ? *reinterpret_cast<const float4*>(
                                                 decay_tok + t * decay_row + head * e + i)
                                           : make_float4(g, g, g, g);
@@ -127,6 +139,7 @@ linear_scan_kernel(const void* __restrict__ a_src, int a_dtype, int a_row, int a
                 float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (col0 + j < f)                      // f is a multiple of four here
                     x = load4(v_src, v_dtype, t * v_row + v_off + head * f + col0 + j);
+                if (act) x = silu4(x);
                 *reinterpret_cast<float4*>(v_s + tt * LS_COLS + j) = x;
             }
         } else {
@@ -138,13 +151,18 @@ linear_scan_kernel(const void* __restrict__ a_src, int a_dtype, int a_row, int a
                 x.y = load_as_float(k_src, t * k_row + k_off + head * e + i, k_dtype);
                 x.z = TOK_DECAY ? decay_tok[t * decay_row + head * e + i] : g;
                 x.w = 0.f;
+                if (act) {
+                    x.x = silu1(x.x);
+                    x.y = silu1(x.y);
+                }
                 akw_s[u] = x;
             }
             for (int u = threadIdx.x; u < nb * LS_COLS; u += LS_THREADS) {
                 const int tt = u / LS_COLS, j = u - tt * LS_COLS;
                 const size_t t = (size_t)(t0 + b0 + tt);
-                v_s[u] = col0 + j < f
+                const float x = col0 + j < f
                     ? load_as_float(v_src, t * v_row + v_off + head * f + col0 + j, v_dtype) : 0.f;
+                v_s[u] = act ? silu1(x) : x;
             }
         }
         __syncthreads();
@@ -225,6 +243,28 @@ scan_finish_kernel(const float* __restrict__ o, const T* __restrict__ gate, int 
     }
 }
 
+// One block a token: the norm runs over the token's whole row of heads.
+template <typename T>
+__global__ void __launch_bounds__(256)
+scan_finish_row_kernel(const float* __restrict__ o, const T* __restrict__ gate, int gate_row,
+                       int gate_off, const float* __restrict__ w, float eps, float out_scale,
+                       T* __restrict__ out, long long out_row, int width) {
+    chain_release();
+    __shared__ float scratch[33];
+    const int t = blockIdx.x;
+    chain_wait();
+    const float* row = o + (size_t)t * width;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) ss = fmaf(row[j], row[j], ss);
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)width + eps);
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        const float z = Elem<T>::load(gate + (size_t)t * gate_row + gate_off + j);
+        float v = row[j] * inv;
+        if (w) v *= w[j];
+        Elem<T>::store(out + (size_t)t * out_row + j, v * (1.0f / (1.0f + expf(-z))) * out_scale);
+    }
+}
+
 // One block a token; thread (head, i) rotates the pair (i, i + dims/2) of q and of k.
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -295,7 +335,8 @@ int launch_scan(dim3 grid, size_t smem, cudaStream_t stream, const void* a_src, 
                 const void* v_src, int v_dtype, int v_row, int v_off, const float* decay_tok,
                 int decay_row, const float* decay_head, const void* bonus, int bonus_dtype,
                 int read_first, const int* cu_q, const int* state_slot, float* state,
-                long long state_stride, int n_heads, int e, int f, int tokens_a_pass, float* out) {
+                long long state_stride, int n_heads, int e, int f, int tokens_a_pass, float* out,
+                int act) {
     auto kernel = decay_tok ? linear_scan_kernel<RPT, true> : linear_scan_kernel<RPT, false>;
     if (smem > 48 * 1024) {
         const int rc = (int)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -305,7 +346,7 @@ int launch_scan(dim3 grid, size_t smem, cudaStream_t stream, const void* a_src, 
     MLS_LAUNCH(kernel, grid, dim3(LS_THREADS), smem, stream, a_src, a_dtype, a_row, a_off, k_src,
                k_dtype, k_row, k_off, v_src, v_dtype, v_row, v_off, decay_tok, decay_row,
                decay_head, bonus, bonus_dtype, read_first, cu_q, state_slot, state, state_stride,
-               n_heads, e, f, tokens_a_pass, out);
+               n_heads, e, f, tokens_a_pass, out, act);
     return launch_status();
 }
 }  // namespace
@@ -316,7 +357,7 @@ MLS_API int mls_linear_scan(const void* a_src, int a_dtype, int a_row, int a_off
                             const float* decay_tok, int decay_row, const float* decay_head,
                             const void* bonus, int bonus_dtype, int read_first, const int* cu_q,
                             const int* state_slot, float* state, long long state_stride,
-                            int n_requests, int n_heads, int e, int f, float* out,
+                            int n_requests, int n_heads, int e, int f, float* out, int act,
                             cudaStream_t stream) {
     if (n_requests <= 0) return 0;
     if (e <= 0 || f <= 0 || e > 32 * LS_GROUPS || (!decay_tok == !decay_head))
@@ -329,7 +370,7 @@ MLS_API int mls_linear_scan(const void* a_src, int a_dtype, int a_row, int a_off
     return launch_scan<R>(grid, smem, stream, a_src, a_dtype, a_row, a_off, k_src, k_dtype, k_row, \
                           k_off, v_src, v_dtype, v_row, v_off, decay_tok, decay_row, decay_head,  \
                           bonus, bonus_dtype, read_first, cu_q, state_slot, state, state_stride,  \
-                          n_heads, e, f, tokens_a_pass, out)
+                          n_heads, e, f, tokens_a_pass, out, act)
     if (rpt <= 2) LS_GO(2);
     if (rpt <= 4) LS_GO(4);
     if (rpt <= 8) LS_GO(8);
@@ -352,6 +393,22 @@ MLS_API int mls_scan_finish(const float* o, const void* gate, int act_dtype, int
         MLS_LAUNCH((scan_finish_kernel<float>), dim3(blocks), dim3(128), 0, stream, o,
                    (const float*)gate, gate_row, gate_off, w, w_dtype, eps, (float*)out, n_tokens,
                    n_heads, f);
+    return launch_status();
+}
+
+MLS_API int mls_scan_finish_row(const float* o, const void* gate, int act_dtype, int gate_row,
+                                int gate_off, const float* w, float eps, float out_scale,
+                                void* out, long long out_row, int n_tokens, int width,
+                                cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (act_dtype == MLS_BF16)
+        MLS_LAUNCH((scan_finish_row_kernel<__nv_bfloat16>), dim3(n_tokens), dim3(256), 0, stream, o,
+                   (const __nv_bfloat16*)gate, gate_row, gate_off, w, eps, out_scale,
+                   (__nv_bfloat16*)out, out_row, width);
+    else
+        MLS_LAUNCH((scan_finish_row_kernel<float>), dim3(n_tokens), dim3(256), 0, stream, o,
+                   (const float*)gate, gate_row, gate_off, w, eps, out_scale, (float*)out, out_row,
+                   width);
     return launch_status();
 }
 

@@ -123,7 +123,7 @@ class Ops:
         self._libs: list = []                    # every kernel library in use
         self._chained = True                     # what the libraries were last told
         core = self._load("core")
-        self._embed = _decl(core, "mls_embed", [_P, _P, _I, _P, _I, _I, _I, _F, _P, _P])
+        self._embed = _decl(core, "mls_embed", [_P, _P, _I, _P, _I, _I, _I, _F, _P, _P, _P, _P])
         self._add_rmsnorm = _decl(core, "mls_add_rmsnorm",
                                   [_P, _P, _I, _P, _I, _F, _P, _I, _I, _I, _P, _I, _LL, _P, _P])
         self._gemm_f32 = _decl(core, "mls_gemm_f32", [_P, _I, _P, _P, _I, _I, _I, _P])
@@ -132,7 +132,7 @@ class Ops:
                                   _LL, _I, _P, _I, _LL, _P, _P])
         self._attention_simt = _decl(core, "mls_attention_simt",
                                      [_P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I,
-                                      _I, _F, _I, _F, _LL, _P, _P])
+                                      _I, _F, _I, _F, _LL, _P, _P, _I, _LL, _P])
         self._swiglu = _decl(core, "mls_swiglu", [_P, _P, _I, _I, _I, _P])
         self._clamped_glu = _decl(core, "mls_clamped_glu", [_P, _P, _I, _I, _I, _F, _F, _P])
         self._unary_act = _decl(core, "mls_unary_act", [_P, _I, _P, _I, _LL, _I, _P, _I, _I, _P])
@@ -214,14 +214,24 @@ class Ops:
                                                                 f"status {code}"))
 
     # ------------------------------------------------------------------ kernels
-    def embed(self, token_ids, table, x, vocab: int, scale: float = 1.0) -> None:
+    def embed(self, token_ids, table, x, vocab: int, scale: float = 1.0, positions=None,
+              freq=None) -> None:
+        """``x[t] = table[token[t]] * scale``; with ``freq`` (float64, one a pair of entries)
+        plus the sinusoidal vector of ``positions[t]``: sine at 2i, cosine at 2i + 1 of
+        ``position * freq[i]``."""
         t, d = x.shape
+        _need(freq is None or (freq.dtype == torch.float64 and freq.numel() >= (d + 1) // 2
+                               and freq.is_contiguous() and positions is not None
+                               and positions.dtype == torch.int32 and positions.numel() >= t),
+              "embed: positions and one float64 frequency a pair of entries")
         _need(x.dtype == torch.float32 and x.is_contiguous(), "embed: x must be float32")
         _need(table.shape == (vocab, d) and table.is_contiguous(), "embed: bad table")
         _need(token_ids.dtype == torch.int32 and token_ids.numel() >= t, "embed: bad ids")
         self.launches += 1
         _check(self._embed(_ptr(token_ids), _ptr(table), _code(table.dtype), _ptr(x), t, d,
-                           vocab, float(scale), _ptr(self.status), self._stream()), "embed")
+                           vocab, float(scale), _ptr(self.status),
+                           _ptr(positions) if freq is not None else None, _ptr(freq),
+                           self._stream()), "embed")
 
     def _delta_args(self, delta, t: int, d: int, what: str):
         """(pointer, type code, parts, part stride) of a pending residual delta."""
@@ -570,19 +580,29 @@ class Ops:
 
     def paged_attention(self, qkv, out, cache, step, n_heads: int, n_kv: int, hd: int,
                         scale: float, window: int, plan=None, softcap: float = 0.0,
-                        sink=None) -> None:
-        """Attention of the step's tokens over the pages.  ``softcap`` c > 0: scores become
+                        sink=None, slopes=None, keep_first: int = 0, simt: bool = False) -> None:
+        """Attention of the step's tokens over the pages.  ``slopes`` (float32 [n_heads]): the
+        score of head h loses ``slopes[h] * (position - key's position)``.  ``keep_first``: a
+        window does not hide the sequence's first so many keys.  ``out`` may be a block of
+        columns of a wider buffer.  The tensor-core kernels take none of the three: such a call
+        (or one with ``simt``, from a mixer that planned for it) runs on the one-warp-per-row
+        kernel.  ``softcap`` c > 0: scores become
         ``c * tanh(score / c)`` before the softmax.  ``sink`` (float32 [n_heads]): the softmax's
         denominator of head h also holds ``exp(sink[h])``, a term without key or value.  ``plan`` (the mixer's, from
         ``attention_facts``): ``n_tiles`` / ``n_tiles_tc`` / ``n_tiles_tc_wide`` tiles of the
         requests that are not small, ``any_small``, ``n_split`` context splits for the small ones."""
         g = step.groups[cache.group]
         t = step.n_tokens
-        _need(out.shape == (t, n_heads * hd) and out.is_contiguous(), "attention: bad out")
+        _need(out.shape == (t, n_heads * hd) and out.stride(1) == 1, "attention: bad out")
         _need(cache.k_pool.dtype == qkv.dtype, "attention: cache and activations differ")
+        _need(slopes is None or (slopes.dtype == torch.float32 and slopes.shape == (n_heads,)
+                                 and slopes.is_contiguous()), "attention: slopes are float32 [heads]")
+        keep_first = int(keep_first or 0) if window else 0
+        plain = (slopes is None and keep_first == 0 and out.stride(0) == n_heads * hd
+                 and not simt)
         _need(sink is None or (sink.dtype == torch.float32 and sink.shape == (n_heads,)
                                and sink.is_contiguous()), "attention: sinks are float32 [heads]")
-        if self.attention_tensor_cores(hd) and qkv.dtype == torch.bfloat16:
+        if self.attention_tensor_cores(hd) and qkv.dtype == torch.bfloat16 and plain:
             fns = self._attention_libs.get(hd)
             _need(fns is not None, f"attention kernels for head size {hd} were not required")
             fn, tc = fns
@@ -625,7 +645,8 @@ class Ops:
             _ptr(qkv), _ptr(out), _code(qkv.dtype), _ptr(cache.k_pool), _ptr(cache.v_pool),
             _ptr(g.block_table), g.max_blocks, _ptr(step.positions), _ptr(step.req_of_token),
             t, n_heads, n_kv, hd, g.block_size, float(scale), int(window), float(softcap),
-            cache.k_pool.shape[1], _ptr(sink), self._stream()), "attention_simt")
+            cache.k_pool.shape[1], _ptr(sink), _ptr(slopes), keep_first, out.stride(0),
+            self._stream()), "attention_simt")
 
     def _split_launches(self, n_split: int, tma: bool, n_ctas: int) -> int:
         """Kernels the context-split attention launches: two to eight splits merge inside
@@ -751,15 +772,16 @@ class Ops:
         elif name == "experts":
             fns = {"tile_rows": _decl(lib, "mls_expert_tile_rows", []),
                    "topk": _decl(lib, "mls_route_topk",
-                                 [_P, _I, _I, _I, _I, _I, _P, _F, _P, _P, _P]),
+                                 [_P, _I, _I, _I, _I, _I, _I, _P, _F, _I, _I, _P, _P, _P]),
                    "sort": _decl(lib, "mls_route_sort",
                                  [_P, _I, _I, _I, _P, _P, _P, _P, _I, _P, _P]),
                    "glu": _decl(lib, "mls_expert_glu",
-                                [_P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _P]),
+                                [_P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _F,
+                                 _P]),
                    "down": _decl(lib, "mls_expert_down",
                                  [_P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _P]),
                    "combine": _decl(lib, "mls_expert_combine",
-                                    [_P, _I, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _P])}
+                                    [_P, _I, _P, _I, _P, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P])}
         elif name == "shortconv":
             fns = {"qk": _decl(lib, "mls_qk_conv_norm_rope_store",
                                [_P, _I, _LL, _P, _P, _I, _P, _P, _I, _F, _P, _LL, _I, _P, _P, _P, _P,
@@ -769,10 +791,23 @@ class Ops:
                                        _P]),
                    "tail": _decl(lib, "mls_tail_update",
                                  [_P, _I, _I, _I, _P, _I, _P, _LL, _I, _I, _P, _P, _I, _P])}
+        elif name == "headprep":
+            fns = {"prep": _decl(lib, "mls_head_prep_store",
+                                 [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _F, _F, _I, _F, _P, _P, _P,
+                                  _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P])}
+        elif name == "side":
+            fns = {"settle_cast": _decl(lib, "mls_settle_cast",
+                                        [_P, _P, _I, _I, _LL, _P, _I, _I, _I, _P]),
+                   "gelu_gate": _decl(lib, "mls_gelu_gate_rows",
+                                      [_P, _P, _I, _I, _I, _P, _I, _P, _I, _I, _I, _I, _P, _P]),
+                   "rms_scale": _decl(lib, "mls_rms_scale",
+                                      [_P, _I, _I, _LL, _P, _F, _P, _I, _I, _P])}
         elif name == "scan":
             fns = {"scan": _decl(lib, "mls_linear_scan",
                                  [_P, _I, _I, _I, _P, _I, _I, _I, _P, _I, _I, _I, _P, _I, _P, _P,
-                                  _I, _I, _P, _P, _P, _LL, _I, _I, _I, _I, _P, _P]),
+                                  _I, _I, _P, _P, _P, _LL, _I, _I, _I, _I, _P, _I, _P]),
+                   "finish_row": _decl(lib, "mls_scan_finish_row",
+                                       [_P, _P, _I, _I, _I, _P, _F, _F, _P, _LL, _I, _I, _P]),
                    "finish": _decl(lib, "mls_scan_finish",
                                    [_P, _P, _I, _I, _I, _P, _I, _F, _P, _I, _I, _I, _P]),
                    "rotate": _decl(lib, "mls_rotate_rows",
@@ -932,21 +967,31 @@ class Ops:
             self._stream()), "mlstm_finish")
 
     def route(self, logits, top: int, renorm: bool, work: dict, softmax: bool = False,
-              correction=None, renorm_eps: float = 0.0, n_real=None) -> None:
+              correction=None, renorm_eps: float = 0.0, n_real=None, groups=None,
+              n_outputs=None) -> None:
         """Choose and sort: from float32 router ``logits [T, E]`` the ``top`` outputs a token
         with the largest score (sigmoid, or ``softmax`` over all outputs) plus ``correction``
         (float32 [E], in the choice only), the scores themselves as weights (``renorm``:
         divided by their sum + ``renorm_eps``), then the (token, choice) slots ordered by
         expert.  Outputs from ``n_real`` on stand for experts without weights and get no
-        tiles.  ``work`` holds the int32 / float32 arrays (``expert_work``)."""
-        t, n_experts = logits.shape
+        tiles.  ``groups = (count, keep)``: the outputs form ``count`` equal groups of
+        neighbours, and only those of the ``keep`` groups whose two largest choice scores have
+        the largest sum can be chosen.  ``n_outputs``: the first so many columns of a wider
+        ``logits`` row are the router's.  ``work`` holds the int32 / float32 arrays
+        (``expert_work``)."""
+        t, row = logits.shape
+        n_experts = row if n_outputs is None else int(n_outputs)
+        n_groups, keep = (int(groups[0]), int(groups[1])) if groups else (1, 1)
+        _need(n_experts <= row and n_groups >= 1 and n_experts % n_groups == 0
+              and 1 <= keep <= n_groups and n_groups <= 256
+              and top <= keep * (n_experts // n_groups), "route: groups do not fit the outputs")
         _need(logits.dtype == torch.float32 and logits.is_contiguous(), "route: logits")
         _need(correction is None or (correction.dtype == torch.float32 and correction.is_contiguous()
                                      and correction.shape == (n_experts,)), "route: correction")
         fns = self._part_lib("experts")
         self.launches += 2
-        _check(fns["topk"](_ptr(logits), t, n_experts, top, 1 if renorm else 0,
-                           1 if softmax else 0, _ptr(correction), float(renorm_eps),
+        _check(fns["topk"](_ptr(logits), row, t, n_experts, top, 1 if renorm else 0,
+                           1 if softmax else 0, _ptr(correction), float(renorm_eps), n_groups, keep,
                            _ptr(work["idx"]), _ptr(work["weight"]), self._stream()), "route_topk")
         _check(fns["sort"](_ptr(work["idx"]), t * top, n_experts,
                            n_experts if n_real is None else int(n_real), _ptr(work["order"]),
@@ -965,8 +1010,11 @@ class Ops:
         weights (the sums are the same either way)."""
         return 1 if n_slots >= 64 * n_experts else 0
 
-    def expert_glu(self, h, w_gate_up, y, work: dict, top: int, scale_in: bool) -> None:
-        """``y[p] = silu(Wg[e] a) * (Wu[e] a)`` for the sorted slots; ``w_gate_up [E, 2F, K]``."""
+    def expert_glu(self, h, w_gate_up, y, work: dict, top: int, scale_in: bool,
+                   alpha: float = 1.0, limit: float = 0.0) -> None:
+        """``y[p] = silu(Wg[e] a) * (Wu[e] a)`` for the sorted slots; ``w_gate_up [E, 2F, K]``.
+        ``limit`` > 0: the clamped unit ``g' * sigmoid(alpha g') * (u' + 1)`` with
+        ``g' = min(g, limit)``, ``u' = clamp(u, -limit, limit)`` instead."""
         n_experts, f2, k = w_gate_up.shape
         _need(h.dtype == w_gate_up.dtype == y.dtype and h.is_contiguous() and y.is_contiguous()
               and w_gate_up.is_contiguous() and h.shape[1] == k and y.shape[1] == f2 // 2,
@@ -976,7 +1024,8 @@ class Ops:
             _ptr(h), _ptr(w_gate_up), _ptr(y), _code(h.dtype), _ptr(work["order"]),
             _ptr(work["offsets"]), _ptr(work["tile_expert"]), _ptr(work["tile_row0"]),
             work["max_tiles"], _ptr(work["weight"]), top, 1 if scale_in else 0, f2 // 2, k,
-            self._many_rows(y.shape[0], n_experts), self._stream()), "expert_glu")
+            self._many_rows(y.shape[0], n_experts), float(alpha), float(limit), self._stream()),
+            "expert_glu")
 
     def expert_down(self, y, w_down, per_slot, work: dict, top: int, scale_out: bool) -> None:
         """``per_slot[slot] = Wd[e] y[p]`` (float32); ``w_down [E, D, F]``."""
@@ -992,10 +1041,11 @@ class Ops:
             self._many_rows(y.shape[0], n_experts), self._stream()), "expert_down")
 
     def expert_combine(self, per_slot, top: int, shared, delta, work=None, n_real=None,
-                       h=None) -> None:
+                       h=None, shared_gate=None) -> None:
         """``delta[t] = sum_j per_slot[t * top + j] + shared[t]``; with ``n_real`` a choice of
         an output from ``n_real`` on adds ``weight * h[t]`` instead (an expert that returns
-        its input)."""
+        its input).  ``shared_gate``: a float32 column (one number a token, any row stride);
+        the shared addend is multiplied by its sigmoid."""
         t, d = delta.shape
         _need(per_slot.shape == (t * top, d) and delta.is_contiguous(), "expert_combine: shapes")
         _need(shared is None or (shared.shape == (t, d) and shared.is_contiguous()),
@@ -1005,10 +1055,14 @@ class Ops:
             _need(work is not None and h is not None and h.shape == (t, d) and h.is_contiguous()
                   and h.dtype == delta.dtype, "expert_combine: identity experts need h and the routing")
             idx, weight = work["idx"], work["weight"]
+        _need(shared_gate is None or (shared is not None and shared_gate.dtype == torch.float32
+                                      and shared_gate.dim() == 1 and shared_gate.shape[0] == t),
+              "expert_combine: the shared addend's gate is one float32 number a token")
         self.launches += 1
         _check(self._part_lib("experts")["combine"](
             _ptr(per_slot), top, _ptr(shared), _code(shared.dtype) if shared is not None else 0,
-            _ptr(idx), _ptr(weight), int(n_real or 0), _ptr(h),
+            _ptr(idx), _ptr(weight), int(n_real or 0), _ptr(h), _ptr(shared_gate),
+            shared_gate.stride(0) if shared_gate is not None else 0,
             _ptr(delta), _code(delta.dtype), t, d, self._stream()), "expert_combine")
 
     def add_tanh_norm(self, x, delta, norm, h, post=None, bias=None, rows=None, n_rows: int = 0,
@@ -1213,14 +1267,15 @@ class Ops:
         _need(0 < e <= 256, f"the scan kernel keeps up to 256 rows of a head's state, not {e}")
 
     def linear_scan(self, a, k, v, state, step, n_heads: int, e: int, f: int, out,
-                    decay_tok=None, decay_head=None, bonus=None, read_first: bool = False) -> None:
+                    decay_tok=None, decay_head=None, bonus=None, read_first: bool = False,
+                    silu: bool = False) -> None:
         """Walk every request's tokens through the matrix state ``S [e, f]`` of every head.
         ``a``, ``k``, ``v``: (tensor [T, *], first column) of the read vector, keys and
         values.  ``decay_tok [T, H*e]`` float32 (a decay per token and key channel) or
         ``decay_head [H]`` float32 (one a head).  ``read_first``: the token reads
         ``S + diag(bonus) k v^T`` and the state moves on afterwards; else the state takes
-        the token in and is then read.  ``state [slots, >= H*e*f]`` float32, ``out [T, H*f]``
-        float32."""
+        the token in and is then read.  ``silu``: a, k and v pass through ``z * sigmoid(z)`` as
+        they are read.  ``state [slots, >= H*e*f]`` float32, ``out [T, H*f]`` float32."""
         t = step.n_tokens
         for (src, off), width in ((a, e), (k, e), (v, f)):
             _need(src.is_contiguous() and src.shape[0] >= t
@@ -1244,7 +1299,8 @@ class Ops:
             _ptr(decay_tok), n_heads * e, _ptr(decay_head), _ptr(bonus),
             _code(bonus.dtype) if bonus is not None else 0, 1 if read_first else 0,
             _ptr(step.cu_q), _ptr(step.state_slot), _ptr(state), state.stride(0),
-            step.n_requests, n_heads, e, f, _ptr(out), self._stream()), "linear_scan")
+            step.n_requests, n_heads, e, f, _ptr(out), 1 if silu else 0, self._stream()),
+            "linear_scan")
 
     def scan_finish(self, o, gate, gate_off: int, weight, eps: float, out, n_heads: int,
                     f: int) -> None:
@@ -1260,6 +1316,102 @@ class Ops:
             _ptr(o), _ptr(gate), _code(gate.dtype), gate.shape[1], gate_off, _ptr(weight),
             _code(weight.dtype) if weight is not None else 0, float(eps), _ptr(out), t, n_heads,
             f, self._stream()), "scan_finish")
+
+    def scan_finish_row(self, o, gate, gate_off: int, weight, eps: float, out,
+                        out_scale: float = 1.0) -> None:
+        """``out = o / rms(o over the whole row) * weight * sigmoid(gate) * out_scale``;
+        ``weight`` float32 or None; ``out`` may be a block of columns of a wider buffer."""
+        t, width = o.shape
+        _need(o.dtype == torch.float32 and o.is_contiguous() and out.shape == (t, width)
+              and out.stride(1) == 1 and out.dtype == gate.dtype and gate.is_contiguous()
+              and gate.shape[1] >= gate_off + width, "scan_finish_row: operands")
+        _need(weight is None or (weight.shape == (width,) and weight.dtype == torch.float32
+                                 and weight.is_contiguous()), "scan_finish_row: bad weight")
+        self.launches += 1
+        _check(self._part_lib("scan")["finish_row"](
+            _ptr(o), _ptr(gate), _code(gate.dtype), gate.shape[1], gate_off, _ptr(weight),
+            float(eps), float(out_scale), _ptr(out), out.stride(0), t, width, self._stream()),
+            "scan_finish_row")
+
+    def head_prep_store(self, proj, cols: tuple, biases, norms, eps: float, q_temp, v_scale: float,
+                        q_out, cache, step, n_heads: int, n_kv: int, e: int, f: int,
+                        hd: int) -> None:
+        """From the float32 projection ``proj [T, W]`` with q, k and v heads (``e``, ``e`` and
+        ``f`` entries each) from the columns ``cols = (q, k, v)`` on: add ``biases = (b_q, b_k,
+        b_v)`` (float32, or None), RMS-normalise every q and k head with ``norms = (w_q, w_k)``
+        (float32 [e], or None), multiply q by ``1 + coef * ln(floor((p + 1) / every) + 1)``
+        (``q_temp = (coef, every)`` or None) and v by ``v_scale``; q goes to ``q_out`` (head h
+        at column ``h * hd``), k and v into the pages at the step's slots, every head padded
+        with zeros to ``hd`` entries; the rest of a page a request enters is cleared."""
+        g = step.groups[cache.group]
+        t = step.n_tokens
+        pool = cache.k_pool
+        _need(proj.dtype == torch.float32 and proj.is_contiguous() and proj.shape[0] == t
+              and proj.shape[1] >= max(cols[0] + n_heads * e, cols[1] + n_kv * e,
+                                       cols[2] + n_kv * f), "head_prep_store: bad projection")
+        _need(pool.is_contiguous() and cache.v_pool.is_contiguous() and pool.shape[0] == n_kv
+              and pool.shape[3] == hd and hd >= max(e, f) and q_out.dtype == pool.dtype
+              and q_out.is_contiguous() and q_out.shape[0] >= t and q_out.shape[1] >= n_heads * hd,
+              "head_prep_store: bad pool or output")
+        vecs = [v for v in (tuple(biases or ()) + tuple(norms or ())) if v is not None]
+        _need(all(v.dtype == torch.float32 and v.is_contiguous() for v in vecs),
+              "head_prep_store: float32 vectors")
+        b_q, b_k, b_v = biases if biases else (None, None, None)
+        w_q, w_k = norms if norms else (None, None)
+        _need(b_q is None or (b_q.numel() == n_heads * e and b_k.numel() == n_kv * e
+                              and b_v.numel() == n_kv * f), "head_prep_store: bad biases")
+        _need(w_q is None or (w_q.numel() == e and w_k.numel() == e), "head_prep_store: bad norms")
+        coef, every = q_temp if q_temp else (0.0, 0)
+        self.launches += 1
+        _check(self._part_lib("headprep")["prep"](
+            _ptr(proj), proj.shape[1], cols[0], cols[1], cols[2], _ptr(b_q), _ptr(b_k), _ptr(b_v),
+            _ptr(w_q), _ptr(w_k), float(eps), float(coef), int(every), float(v_scale),
+            _ptr(step.positions), _ptr(g.slot_map), _ptr(q_out), q_out.shape[1], _code(pool.dtype),
+            _ptr(pool), _ptr(cache.v_pool), g.block_size, pool.shape[1], t, n_heads, n_kv, e, f,
+            hd, 1 if cache.writes else 0, _ptr(self.status), self._stream()), "head_prep_store")
+
+    def settle_cast(self, x, delta, out) -> None:
+        """``x += delta`` (a tensor, ``SplitParts`` or None); ``out = x`` in ``out``'s type."""
+        t, d = x.shape
+        _need(x.dtype == torch.float32 and x.is_contiguous() and out.shape == (t, d)
+              and out.is_contiguous(), "settle_cast: operands")
+        dp, dcode, parts, stride = self._delta_args(delta, t, d, "settle_cast")
+        self.launches += 1
+        _check(self._part_lib("side")["settle_cast"](
+            _ptr(x), dp, dcode, parts, stride, _ptr(out), _code(out.dtype), t, d, self._stream()),
+            "settle_cast")
+        if isinstance(delta, SplitParts):
+            delta.release()
+
+    def gelu_gate_rows(self, z, table, col0: int, token_ids, out, n_real=None) -> None:
+        """``out[t, c] = gelu_tanh(z[t, c]) * table[token[t], col0 + c]`` for the first
+        ``n_real`` columns (all, if None), zeros in the others; ``z`` float32."""
+        t, dim = z.shape
+        n_real = dim if n_real is None else int(n_real)
+        _need(z.dtype == torch.float32 and z.is_contiguous() and out.shape == (t, dim)
+              and out.is_contiguous() and table.is_contiguous() and table.dim() == 2
+              and 0 <= col0 and n_real <= dim and col0 + n_real <= table.shape[1]
+              and token_ids.dtype == torch.int32 and token_ids.numel() >= t,
+              "gelu_gate_rows: operands")
+        self.launches += 1
+        _check(self._part_lib("side")["gelu_gate"](
+            _ptr(z), _ptr(table), _code(table.dtype), table.shape[1], col0, _ptr(token_ids),
+            table.shape[0], _ptr(out), _code(out.dtype), t, dim, n_real, _ptr(self.status),
+            self._stream()), "gelu_gate_rows")
+
+    def rms_scale(self, y, weight, eps: float, out) -> None:
+        """``out[t] = y[t] / sqrt(mean(y[t]^2) + eps) * weight`` in float32; ``y`` a tensor or
+        ``SplitParts``."""
+        t, d = out.shape
+        _need(out.dtype == torch.float32 and out.is_contiguous() and weight.shape == (d,)
+              and weight.dtype == torch.float32 and weight.is_contiguous(), "rms_scale: operands")
+        dp, dcode, parts, stride = self._delta_args(y, t, d, "rms_scale")
+        self.launches += 1
+        _check(self._part_lib("side")["rms_scale"](
+            dp, dcode, parts, stride, _ptr(weight), float(eps), _ptr(out), t, d, self._stream()),
+            "rms_scale")
+        if isinstance(y, SplitParts):
+            y.release()
 
     def rotate_rows(self, src, q_off: int, k_off: int, positions, freq, dims: int,
                     k_scale: float, out, n_heads: int, e: int) -> None:

@@ -49,6 +49,8 @@ MODULES = {
     "experts": ["experts.cu"],
     "shortconv": ["short_conv.cu"],
     "scan": ["linear_scan.cu"],
+    "headprep": ["head_prep.cu"],
+    "side": ["side_input.cu"],
 }
 
 
@@ -61,7 +63,7 @@ def all_modules(head_sizes=()) -> list:
         out.append(("gemm", {}))
     out.append(("argmax_static", {}))
     out += [(name, {}) for name in ("layernorm", "tanhnorm", "latent", "mlstm", "experts",
-                                    "shortconv", "scan")]
+                                    "shortconv", "scan", "headprep", "side")]
     return out
 
 

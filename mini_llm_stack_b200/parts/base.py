@@ -57,11 +57,13 @@ class PagedKV:
 
     ``shared_kv``: one pool serves as keys and as values (a mixer that attends over a
     single cached vector a token, such as a latent); the handle's ``k_pool`` and
-    ``v_pool`` are then the same tensor."""
+    ``v_pool`` are then the same tensor.  ``keep_first``: with a window, the sequence's
+    first so many tokens stay readable for good (their pages are never given back)."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     shared_kv: bool = False
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)

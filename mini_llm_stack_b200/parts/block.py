@@ -31,17 +31,25 @@ def under_prefix(tensors: dict, prefix: str) -> dict:
 
 
 class PreNormBlock(Part):
+    tail = None
+
     def __init__(self, mixer_norm, mixer, ffn_norm, ffn,
-                 names=("attn_norm", "attn", "mlp_norm", "mlp")):
+                 names=("attn_norm", "attn", "mlp_norm", "mlp"), tail=None):
+        """``tail``: a part that runs last, on the stream itself (``forward(stream, step)``:
+        it settles what is pending and pushes its own delta); its prefix is a fifth name."""
         self.mixer_norm, self.mixer = mixer_norm, mixer
         self.ffn_norm, self.ffn = ffn_norm, ffn
+        self.tail = tail
         self.names = tuple(names)
+        if tail is not None and len(self.names) < 5:
+            raise ValueError("a block with a tail needs a fifth name, the tail's prefix")
 
     def _named_parts(self):
         """(prefix, part) of the parts there are; a block without a feed-forward
         (``ffn`` None) has no second norm either."""
         return [(n, p) for n, p in zip(self.names, (self.mixer_norm, self.mixer,
-                                                    self.ffn_norm, self.ffn)) if p is not None]
+                                                    self.ffn_norm, self.ffn, self.tail))
+                if p is not None]
 
     def tensor_specs(self) -> dict:
         out = {}
@@ -78,10 +86,11 @@ class PreNormBlock(Part):
             delta, vec = delta
             stream.push_more(vec=vec)
         stream.push(delta)
-        if self.ffn is None:
-            return
-        h = self.ffn_norm.forward(stream)
-        stream.push(self.ffn.forward(h, step))
+        if self.ffn is not None:
+            h = self.ffn_norm.forward(stream)
+            stream.push(self.ffn.forward(h, step))
+        if self.tail is not None:
+            self.tail.forward(stream, step)
 
 
 class SandwichBlock(PreNormBlock):

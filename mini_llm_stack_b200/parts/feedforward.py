@@ -171,14 +171,21 @@ class RoutedExperts(FeedForward):
     where a weight multiplies: "input" (the expert sees ``w * h``) or "output".  The last
     ``identity`` router outputs stand for experts without tensors that return their input
     (times the weight).  A ``shared`` feed-forward, if any, runs for every token and is
-    added.  Tensors: ``router`` [E + identity, d] and ``e<i>.gate / up / down`` for each of
-    the E experts; the shared part's under ``shared``."""
+    added; with ``shared_gate`` it is first multiplied by ``sigmoid(w_sg . h)``, one number a
+    token (tensor ``shared.sg`` [1, d]).  ``groups = (count, keep)``: the router's outputs form
+    ``count`` equal groups of neighbours, a group's score is the sum of its two largest choice
+    scores, and only outputs of the ``keep`` best groups can be chosen.  ``limit`` > 0: the
+    experts are clamped units, ``g' * sigmoid(alpha g') * (u' + 1)`` with ``g' = min(g, limit)``
+    and ``u' = clamp(u, -limit, limit)``, instead of ``silu(g) * u``.  Tensors: ``router``
+    [E + identity, d] and ``e<i>.gate / up / down`` for each of the E experts; the shared
+    part's under ``shared``."""
 
     decode_capturable = prompt_capturable = True   # routing, sorting and the products stay on the device
 
     def __init__(self, d_model: int, n_experts: int, top: int, expert_size: int, shared=None,
                  weigh: str = "input", renormalise: bool = False, score: str = "sigmoid",
-                 correction: bool = False, identity: int = 0, renorm_eps: float = 0.0):
+                 correction: bool = False, identity: int = 0, renorm_eps: float = 0.0,
+                 groups=None, limit: float = 0.0, alpha: float = 1.0, shared_gate: bool = False):
         if weigh not in ("input", "output"):
             raise ValueError(f"weigh must be 'input' or 'output', not {weigh!r}")
         if score not in ("sigmoid", "softmax"):
@@ -194,6 +201,17 @@ class RoutedExperts(FeedForward):
         self.identity, self.renorm_eps = int(identity), float(renorm_eps)
         self.n_outputs = self.n_experts + self.identity
         self.correction = None
+        self.groups = (int(groups[0]), int(groups[1])) if groups else None
+        if self.groups is not None:
+            count, keep = self.groups
+            if count < 1 or self.n_outputs % count or not 1 <= keep <= count:
+                raise ValueError("the router's outputs must form equal groups, of which some are kept")
+            if self.top > keep * (self.n_outputs // count):
+                raise ValueError("the kept groups hold fewer outputs than a token takes")
+        self.limit, self.alpha = float(limit), float(alpha)
+        self.shared_gate = bool(shared_gate)
+        if self.shared_gate and shared is None:
+            raise ValueError("a gate on the shared expert needs a shared expert")
 
     def tensor_specs(self) -> dict:
         d, f = self.d_model, self.expert_size
@@ -206,12 +224,17 @@ class RoutedExperts(FeedForward):
             out[f"e{i}.down"] = TensorSpec((d, f))
         if self.shared is not None:
             out.update({f"shared.{n}": s for n, s in self.shared.tensor_specs().items()})
+        if self.shared_gate:
+            out["shared.sg"] = TensorSpec((1, d))
         return out
 
     def bind(self, tensors: dict, runtime) -> None:
         self.runtime = runtime
         n = self.n_experts
         self.w_router = tensors["router"].float().contiguous()       # scores are float32
+        if self.shared_gate:
+            # the gate's row rides behind the router's: one float32 product gives both
+            self.w_router = torch.cat([self.w_router, tensors["shared.sg"].float()], 0).contiguous()
         if self.has_correction:
             self.correction = tensors["correction"].float().contiguous()
         self.w_gate_up = torch.stack([torch.cat([tensors[f"e{i}.gate"], tensors[f"e{i}.up"]], 0)
@@ -219,7 +242,7 @@ class RoutedExperts(FeedForward):
         self.w_down = torch.stack([tensors[f"e{i}.down"] for i in range(n)]).contiguous()
         if self.shared is not None:
             self.shared.bind({k[len("shared."):]: v for k, v in tensors.items()
-                              if k.startswith("shared.")}, runtime)
+                              if k.startswith("shared.") and k != "shared.sg"}, runtime)
         runtime.ops.require_part("experts")
 
     def _work(self, t: int) -> dict:
@@ -238,15 +261,17 @@ class RoutedExperts(FeedForward):
     def forward(self, h, step: StepContext):
         rt, ops = self.runtime, self.runtime.ops
         t = h.shape[0]
-        logits = rt.buffer("route_logits", (t, self.n_outputs), torch.float32)
+        logits = rt.buffer("route_logits", (t, self.w_router.shape[0]), torch.float32)
         ops.linear(h, self.w_router, logits)
         work = self._work(t)
         ops.route(logits, self.top, self.renormalise, work, softmax=self.score == "softmax",
-                  correction=self.correction, renorm_eps=self.renorm_eps, n_real=self.n_experts)
+                  correction=self.correction, renorm_eps=self.renorm_eps, n_real=self.n_experts,
+                  groups=self.groups, n_outputs=self.n_outputs)
         n_slots = t * self.top
         y = rt.buffer("expert_act", (n_slots, self.expert_size), rt.act_dtype)
         per_slot = rt.buffer("expert_out", (n_slots, self.d_model), torch.float32)
-        ops.expert_glu(h, self.w_gate_up, y, work, self.top, self.weigh == "input")
+        ops.expert_glu(h, self.w_gate_up, y, work, self.top, self.weigh == "input",
+                       alpha=self.alpha, limit=self.limit)
         ops.expert_down(y, self.w_down, per_slot, work, self.top, self.weigh == "output")
         shared = None
         if self.shared is not None:
@@ -254,9 +279,10 @@ class RoutedExperts(FeedForward):
             if not isinstance(shared, torch.Tensor):
                 shared = shared.float()              # a product left as its K-parts
         delta = rt.buffer("routed_delta", (t, self.d_model), rt.act_dtype)
+        gate = logits[:, self.n_outputs] if self.shared_gate else None
         if self.identity:
             ops.expert_combine(per_slot, self.top, shared, delta, work=work,
-                               n_real=self.n_experts, h=h)
+                               n_real=self.n_experts, h=h, shared_gate=gate)
         else:
-            ops.expert_combine(per_slot, self.top, shared, delta)
+            ops.expert_combine(per_slot, self.top, shared, delta, shared_gate=gate)
         return delta

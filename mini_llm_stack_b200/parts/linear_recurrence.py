@@ -164,3 +164,74 @@ class RetentionMixer(Mixer):
         ops.scan_finish(o, qkvg, 2 * nh * e + nh * f, None, self.eps, y, nh, f)
         delta = rt.buffer("delta", (t, self.d_model), rt.act_dtype)
         return ops.linear_parts(y, self.w_o, delta)
+
+
+class LightningAttention(Mixer):
+    """Linear attention with one constant decay a head and a matrix state per head:
+
+        q, k, v = silu(W_q h), silu(W_k h), silu(W_v h)       (heads of e, e and f entries)
+        S <- decay_head S + k_t v_t^T;   o_t = S^T q_t          (no other scale)
+        out = W_o (rms_norm(o over all heads together) * w * sigmoid(W_g h)) * out_scale
+
+    The state lives in the request's state slot (float32, zero when claimed) and is carried
+    from token to token, so cutting a prompt changes no bit.  Activations enter the scan in
+    float32; decays, state, sums and the norm are float32 in both run types.  With
+    ``project=False`` the mixer has no output projection: ``heads(h, step, cache, out)``
+    leaves the normed, gated and scaled heads in ``out`` (which may be a block of columns of
+    a wider buffer) for a mixer that owns this one."""
+
+    decode_capturable = prompt_capturable = True
+
+    def __init__(self, d_model: int, n_heads: int, qk_dim: int, v_dim: int, decay, eps: float,
+                 out_scale: float = 1.0, project: bool = True):
+        self.d_model, self.n_heads = int(d_model), int(n_heads)
+        self.qk_dim, self.v_dim, self.eps = int(qk_dim), int(v_dim), float(eps)
+        self.decay_values = [float(x) for x in decay]
+        if len(self.decay_values) != self.n_heads:
+            raise ValueError("lightning attention needs one decay a head")
+        self.out_scale, self.project = float(out_scale), bool(project)
+        self.out_width = self.n_heads * self.v_dim
+
+    def tensor_specs(self) -> dict:
+        d, h, e, f = self.d_model, self.n_heads, self.qk_dim, self.v_dim
+        out = {"q": TensorSpec((h * e, d)), "k": TensorSpec((h * e, d)),
+               "v": TensorSpec((h * f, d)), "g": TensorSpec((h * f, d)),
+               "norm": TensorSpec((h * f,), kind="vector", init="ones")}
+        if self.project:
+            out["o"] = TensorSpec((d, h * f))
+        return out
+
+    def cache_spec(self):
+        return FixedState((self.n_heads * self.qk_dim * self.v_dim,), torch.float32)
+
+    def bind(self, tensors: dict, runtime) -> None:
+        self.runtime = runtime
+        ops = runtime.ops
+        ops.require_part("scan")
+        ops.require_scan(self.qk_dim)
+        self.w_qkvg = ops.prepare_weight(torch.cat(
+            [tensors["q"], tensors["k"], tensors["v"], tensors["g"]], dim=0))
+        self.g_norm = tensors["norm"].float().contiguous()
+        if self.project:
+            self.w_o = ops.prepare_weight(tensors["o"])
+        self.decay = torch.tensor(self.decay_values, dtype=torch.float32, device=runtime.device)
+
+    def heads(self, h, step: StepContext, cache: CacheHandle, out) -> None:
+        rt, ops = self.runtime, self.runtime.ops
+        t, nh, e, f = step.n_tokens, self.n_heads, self.qk_dim, self.v_dim
+        qkvg = rt.buffer("ret_qkvg", (t, 2 * nh * e + 2 * nh * f), rt.act_dtype)
+        ops.linear(h, self.w_qkvg, qkvg)
+        o = rt.buffer("scan_out", (t, nh * f), torch.float32)
+        ops.linear_scan((qkvg, 0), (qkvg, nh * e), (qkvg, 2 * nh * e), cache.state, step, nh, e, f,
+                        o, decay_head=self.decay, silu=True)
+        ops.scan_finish_row(o, qkvg, 2 * nh * e + nh * f, self.g_norm, self.eps, out,
+                            out_scale=self.out_scale)
+
+    def forward(self, h, step: StepContext, cache: CacheHandle):
+        if not self.project:
+            raise RuntimeError("this mixer has no output projection: its owner calls heads()")
+        rt = self.runtime
+        y = rt.buffer("attn_out", (step.n_tokens, self.out_width), rt.act_dtype)
+        self.heads(h, step, cache, y)
+        delta = rt.buffer("delta", (step.n_tokens, self.d_model), rt.act_dtype)
+        return rt.ops.linear_parts(y, self.w_o, delta)

@@ -90,15 +90,17 @@ class PassProjection(Part):
 
 
 class TokenEmbedding(Part):
-    """``x[t] = E[token[t]] * scale``; no position term.  (The reference has no scaling
-    either: ``scale`` 1, train/model.py:239.)"""
+    """``x[t] = E[token[t]] * scale``, plus the vector of an additive position part
+    (``position``, e.g. ``SinusoidalPositions``) if there is one.  (The reference has neither
+    scaling nor a position term: ``scale`` 1, train/model.py:239.)"""
 
     decode_capturable = prompt_capturable = True
 
     def __init__(self, vocab_size: int, d_model: int, tensor_name: str = "weight",
-                 scale: float = 1.0):
+                 scale: float = 1.0, position=None):
         self.vocab_size, self.d_model = int(vocab_size), int(d_model)
         self.tensor_name, self.scale = tensor_name, float(scale)
+        self.position = position
         self.weight = None
 
     def tensor_specs(self) -> dict:
@@ -107,11 +109,17 @@ class TokenEmbedding(Part):
     def bind(self, tensors: dict, runtime) -> None:
         self.runtime = runtime
         self.weight = tensors[self.tensor_name].contiguous()
+        if self.position is not None:
+            self.position.bind({}, runtime)
 
     def forward(self, step: StepContext, buffer: str = "residual"):
         rt = self.runtime
         x = rt.buffer(buffer, (step.n_tokens, self.d_model), rt.residual_dtype)
-        rt.ops.embed(step.token_ids, self.weight, x, self.vocab_size, self.scale)
+        if self.position is not None:
+            rt.ops.embed(step.token_ids, self.weight, x, self.vocab_size, self.scale,
+                         positions=step.positions, freq=self.position.freq)
+        else:
+            rt.ops.embed(step.token_ids, self.weight, x, self.vocab_size, self.scale)
         return x
 
 

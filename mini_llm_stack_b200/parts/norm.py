@@ -18,19 +18,24 @@ from .base import Norm, ResidualStream, TensorSpec
 class RMSNorm(Norm):
     decode_capturable = prompt_capturable = True   # forward only launches kernels on the current stream
 
-    def __init__(self, dim: int, eps: float, tensor_name: str = "weight"):
-        """``tensor_name``: the local name of the weight ("" = the part's own prefix)."""
+    def __init__(self, dim: int, eps: float, tensor_name: str = "weight", one_plus: bool = False):
+        """``tensor_name``: the local name of the weight ("" = the part's own prefix).
+        ``one_plus``: the weight is stored around zero and multiplies as ``1 + w`` (the sum is
+        taken once, in float32, when the weight is bound)."""
         self.dim = int(dim)
         self.eps = float(eps)
         self.tensor_name = tensor_name
+        self.one_plus = bool(one_plus)
         self.weight = None
 
     def tensor_specs(self) -> dict:
-        return {self.tensor_name: TensorSpec((self.dim,), kind="vector", init="ones")}
+        return {self.tensor_name: TensorSpec((self.dim,), kind="vector",
+                                             init="zeros" if self.one_plus else "ones")}
 
     def bind(self, tensors: dict, runtime) -> None:
         self.runtime = runtime
-        self.weight = tensors[self.tensor_name].contiguous()
+        w = tensors[self.tensor_name]
+        self.weight = (w.float() + 1.0).contiguous() if self.one_plus else w.contiguous()
 
     def forward(self, stream: ResidualStream, rows=None, n_rows: int = 0):
         """Add the pending delta into the stream, return the normalised rows.

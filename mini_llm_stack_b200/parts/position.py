@@ -1,6 +1,7 @@
 """Rotary position encoding: rotate-half pairing over the whole head by table
 (``RotaryPosition``), and a rotation of a head's first entries with either pairing and
-scaled frequencies (``PartialRotary``).
+scaled frequencies (``PartialRotary``); a sinusoidal vector added to the embedding
+(``SinusoidalPositions``).
 
 Reference (train/model.py:36-52): ``inv_freq[i] = theta ** -(2i / head_dim)``
 for i in [0, head_dim/2); ``angle[p, i] = p * inv_freq[i]``; cos and sin tables
@@ -98,6 +99,28 @@ class PartialRotary(PositionEncoding):
         i = torch.arange(self.dims // 2, dtype=torch.float64)
         return torch.pow(torch.tensor(self.base, dtype=torch.float64),
                          -2.0 * i / max(self.dims, 1)) / self.factor
+
+    def bind(self, tensors: dict, runtime) -> None:
+        self.runtime = runtime
+        self.freq = self.frequencies().to(runtime.device).contiguous()
+
+
+class SinusoidalPositions(PositionEncoding):
+    """A vector added to a token's embedding: entry 2i is ``sin(p * base^(-2i/width))`` and
+    entry 2i + 1 the cosine of the same angle, p the token's position.  There is no table and
+    so no bound on the positions: the embedding kernel forms the angle in float64 from the
+    position and this part's float64 frequencies."""
+
+    decode_capturable = prompt_capturable = True
+
+    def __init__(self, width: int, base: float = 10000.0):
+        self.width, self.base = int(width), float(base)
+        self.freq = None
+
+    def frequencies(self):
+        """``base^(-2i/width)`` for every pair of entries, float64 on the host."""
+        i = torch.arange((self.width + 1) // 2, dtype=torch.float64)
+        return torch.pow(torch.tensor(self.base, dtype=torch.float64), -2.0 * i / self.width)
 
     def bind(self, tensors: dict, runtime) -> None:
         self.runtime = runtime
