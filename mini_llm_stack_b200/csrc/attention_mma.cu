@@ -59,7 +59,33 @@ struct Params {
     long long n_pages;                   // pages of the pool: [Hkv, pages, block, HD]
     const float* sink;                   // [H] or nullptr: exp(sink_h) joins the softmax's
                                          // denominator, a term without key or value
+    // (the three below: the kernels without TMA only; the others get none of them)
+    const float* slopes;                 // [H] or nullptr: the score of head h loses
+                                         // slopes[h] * (query position - key position)
+    int keep;                            // with a window: the first so many keys stay visible
+    long long out_stride;                // elements between two tokens' rows of `out`
 };
+
+// The key tiles a block of rows walks: with a window that begins at lo, first the tiles of the
+// kept first keys that lie wholly before the window's first tile, then the tiles from the
+// window's on (kept keys inside those are let through by the rows' masks).
+struct TileRange {
+    int kbase0, keep_tiles, tiles_all;
+};
+__device__ __forceinline__ TileRange tile_range(int lo, int hi, int keep, int bn) {
+    TileRange R;
+    R.kbase0 = (lo / bn) * bn;
+    R.keep_tiles = (keep > 0 && lo > 0) ? min((min(keep, lo) + bn - 1) / bn, R.kbase0 / bn) : 0;
+    R.tiles_all = R.keep_tiles + (hi - R.kbase0) / bn + 1;
+    return R;
+}
+__device__ __forceinline__ int tile_base(const TileRange& R, int t, int bn) {
+    return t < R.keep_tiles ? t * bn : R.kbase0 + (t - R.keep_tiles) * bn;
+}
+// What a row at position p of a head with this slope (log2 domain) loses against key j.
+__device__ __forceinline__ float distance_bias(float slope_log2, int p, int j) {
+    return slope_log2 * (float)(p - j);
+}
 
 // What a sink adds to a row's sum of exponentials taken relative to the maximum m (log2
 // domain): 2^(sink * log2(e) - m).  A row without keys (m = -inf) has no output anyway.
@@ -149,9 +175,9 @@ __device__ __forceinline__ bool is_small(int q_len, int group) { return q_len * 
 // longer contexts.  With a window a small request (at most 16 new tokens) sees at most
 // window + 15 keys, which begin anywhere in a tile.
 __device__ __forceinline__ int tiles_per_split(const int* ctx_len, int n_req, int window, int bn,
-                                               int n_split) {
+                                               int n_split, int keep = 0) {
     int most = (ctx_len[n_req] + bn - 1) / bn;
-    if (window > 0) most = min(most, (window + 15 + bn - 2) / bn + 1);
+    if (window > 0) most = min(most, (window + 15 + bn - 2) / bn + 1 + (keep + bn - 1) / bn);
     return (max(most, 1) + n_split - 1) / n_split;
 }
 
@@ -164,7 +190,7 @@ __device__ __forceinline__ void load_kv_tile(uint8_t* ks, uint8_t* vs, const Par
     for (int idx = threadIdx.x; idx < BN * KCH; idx += NT) {
         const int row = idx / KCH, ch = idx - row * KCH;
         const int j = kbase + row;
-        bool ok = j >= lo && j <= hi;
+        bool ok = (j >= lo || j < P.keep) && j <= hi;
         size_t off = 0;
         if (ok) {
             const int page = table[j / P.block_size];
@@ -227,11 +253,11 @@ __global__ void __launch_bounds__(NT) attention_tile_kernel(const Params P) {
     const int hi = pos0 + i_last;
     const int lo = P.window > 0 ? max(0, pos0 + i_first - P.window + 1) : 0;
     const int* table = P.block_table + (size_t)r * P.max_blocks;
-    const int kbase0 = (lo / BN) * BN;
-    const int n_tiles = (hi - kbase0) / BN + 1;
+    const TileRange R = tile_range(lo, hi, P.keep, BN);
+    const int n_tiles = R.tiles_all;
 
     load_q_rows(qs, P, tok0, kvh, row0, 64, rows);
-    load_kv_tile(kbuf, vbuf, P, table, kvh, kbase0, lo, hi);
+    load_kv_tile(kbuf, vbuf, P, table, kvh, tile_base(R, 0, BN), lo, hi);
     cp_async_commit();
 
     // positions of this thread's two rows (-1: the row does not exist)
@@ -240,6 +266,8 @@ __global__ void __launch_bounds__(NT) attention_tile_kernel(const Params P) {
     const int pB = rB < rows ? pos0 + rB / P.group : -1;
     const int loA = P.window > 0 ? pA - P.window + 1 : 0;
     const int loB = P.window > 0 ? pB - P.window + 1 : 0;
+    const float slA = P.slopes ? P.slopes[kvh * P.group + rA % P.group] * LOG2E : 0.f;
+    const float slB = P.slopes ? P.slopes[kvh * P.group + rB % P.group] * LOG2E : 0.f;
 
     uint32_t qf[HD / 16][4];
     float o[HD / 8][4];
@@ -256,10 +284,10 @@ __global__ void __launch_bounds__(NT) attention_tile_kernel(const Params P) {
 #pragma unroll
             for (int ks = 0; ks < HD / 16; ++ks) ldsm_x4(qf[ks], qa + ks * 32);
         }
-        const int kbase = kbase0 + t * BN;
+        const int kbase = tile_base(R, t, BN);
         if (t + 1 < n_tiles) {
             load_kv_tile(kbuf + ((t + 1) & 1) * TILE_BYTES, vbuf + ((t + 1) & 1) * TILE_BYTES, P,
-                         table, kvh, kbase + BN, lo, hi);
+                         table, kvh, tile_base(R, t + 1, BN), lo, hi);
             cp_async_commit();
         }
         const uint32_t ka = smem_u32(kbuf + (t & 1) * TILE_BYTES);
@@ -288,8 +316,10 @@ __global__ void __launch_bounds__(NT) attention_tile_kernel(const Params P) {
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int jj = j + e;
-                const float a = (jj <= pA && jj >= loA) ? score_log2(s[n][e], P) : -INFINITY;
-                const float b = (jj <= pB && jj >= loB) ? score_log2(s[n][2 + e], P) : -INFINITY;
+                const float a = (jj <= pA && (jj >= loA || jj < P.keep))
+                    ? score_log2(s[n][e], P) - distance_bias(slA, pA, jj) : -INFINITY;
+                const float b = (jj <= pB && (jj >= loB || jj < P.keep))
+                    ? score_log2(s[n][2 + e], P) - distance_bias(slB, pB, jj) : -INFINITY;
                 s[n][e] = a;
                 s[n][2 + e] = b;
                 tmA = fmaxf(tmA, a);
@@ -353,7 +383,7 @@ __global__ void __launch_bounds__(NT) attention_tile_kernel(const Params P) {
         const int row = half ? rB : rA;
         if (row >= rows) continue;
         const int i = row / P.group, g = row - i * P.group;
-        __nv_bfloat16* dst = P.out + (size_t)(tok0 + i) * P.n_heads * HD +
+        __nv_bfloat16* dst = P.out + (size_t)(tok0 + i) * P.out_stride +
                              (size_t)(kvh * P.group + g) * HD + (lane & 3) * 2;
         const float inv = half ? invB : invA;
 #pragma unroll
@@ -387,10 +417,10 @@ __global__ void __launch_bounds__(NT) attention_split_kernel(const Params P) {
     const int hi = ctx - 1;
     const int lo = P.window > 0 ? max(0, pos0 - P.window + 1) : 0;
     const int* table = P.block_table + (size_t)r * P.max_blocks;
-    const int kbase0 = (lo / BN) * BN;
-    const int tiles_all = (hi - kbase0) / BN + 1;
+    const TileRange R = tile_range(lo, hi, P.keep, BN);
+    const int tiles_all = R.tiles_all;
     const int per = P.n_split == 1 ? tiles_all
-        : tiles_per_split(P.ctx_len, P.n_req, P.window, BN, P.n_split);
+        : tiles_per_split(P.ctx_len, P.n_req, P.window, BN, P.n_split, P.keep);
     const int t_begin = split * per, t_end = min(tiles_all, t_begin + per);
     const int n_tiles = max(0, t_end - t_begin);
     if (n_tiles == 0) return;                         // a stretch past the request's end: the merge knows
@@ -400,6 +430,8 @@ __global__ void __launch_bounds__(NT) attention_split_kernel(const Params P) {
     const int pB = rB < rows ? pos0 + rB / P.group : -1;
     const int loA = P.window > 0 ? pA - P.window + 1 : 0;
     const int loB = P.window > 0 ? pB - P.window + 1 : 0;
+    const float slA = P.slopes ? P.slopes[kvh * P.group + rA % P.group] * LOG2E : 0.f;
+    const float slB = P.slopes ? P.slopes[kvh * P.group + rB % P.group] * LOG2E : 0.f;
 
     float o[HD / 8][4];
 #pragma unroll
@@ -413,7 +445,7 @@ __global__ void __launch_bounds__(NT) attention_split_kernel(const Params P) {
         for (int st = 0; st < STAGES - 1; ++st) {
             if (st < n_tiles)
                 load_kv_tile(kbuf + st * TILE_BYTES, vbuf + st * TILE_BYTES, P, table, kvh,
-                             kbase0 + (t_begin + st) * BN, lo, hi);
+                             tile_base(R, t_begin + st, BN), lo, hi);
             cp_async_commit();
         }
     }
@@ -430,10 +462,10 @@ __global__ void __launch_bounds__(NT) attention_split_kernel(const Params P) {
             const int nt = t + STAGES - 1;
             if (nt < n_tiles)
                 load_kv_tile(kbuf + (nt % STAGES) * TILE_BYTES, vbuf + (nt % STAGES) * TILE_BYTES,
-                             P, table, kvh, kbase0 + (t_begin + nt) * BN, lo, hi);
+                             P, table, kvh, tile_base(R, t_begin + nt, BN), lo, hi);
             cp_async_commit();
         }
-        const int kbase = kbase0 + (t_begin + t) * BN + warp * 16;     // this warp's 16 keys
+        const int kbase = tile_base(R, t_begin + t, BN) + warp * 16;   // this warp's 16 keys
         const uint32_t ka = smem_u32(kbuf + (t % STAGES) * TILE_BYTES) + warp * 16 * ROWB;
         const uint32_t va = smem_u32(vbuf + (t % STAGES) * TILE_BYTES) + warp * 16 * ROWB;
 
@@ -454,8 +486,10 @@ __global__ void __launch_bounds__(NT) attention_split_kernel(const Params P) {
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int jj = j + e;
-                const float a = (jj <= pA && jj >= loA) ? score_log2(s[n][e], P) : -INFINITY;
-                const float b = (jj <= pB && jj >= loB) ? score_log2(s[n][2 + e], P) : -INFINITY;
+                const float a = (jj <= pA && (jj >= loA || jj < P.keep))
+                    ? score_log2(s[n][e], P) - distance_bias(slA, pA, jj) : -INFINITY;
+                const float b = (jj <= pB && (jj >= loB || jj < P.keep))
+                    ? score_log2(s[n][2 + e], P) - distance_bias(slB, pB, jj) : -INFINITY;
                 s[n][e] = a;
                 s[n][2 + e] = b;
                 tmA = fmaxf(tmA, a);
@@ -548,7 +582,8 @@ __global__ void __launch_bounds__(NT) attention_split_kernel(const Params P) {
         const float val = l > 0.f ? acc / l : 0.f;
         const size_t unit = (size_t)(tok0 + i) * P.n_heads + (kvh * P.group + g);
         if (P.n_split == 1) {
-            P.out[unit * HD + d] = __float2bfloat16_rn(val);
+            P.out[(size_t)(tok0 + i) * P.out_stride + (size_t)(kvh * P.group + g) * HD + d] =
+                __float2bfloat16_rn(val);
         } else {
             const size_t units = (size_t)P.n_tokens * P.n_heads;
             P.part_o[((size_t)split * units + unit) * HD + d] = val;
@@ -575,10 +610,10 @@ __global__ void attention_merge_kernel(const Params P) {
     __shared__ int parts_here;
     if (threadIdx.x < 32) {
         // the stretches of this request that hold tiles: the others wrote nothing
-        const int per = tiles_per_split(P.ctx_len, P.n_req, P.window, BN, P.n_split);
+        const int per = tiles_per_split(P.ctx_len, P.n_req, P.window, BN, P.n_split, P.keep);
         const int ctx = P.ctx_len[r];
         const int lo = P.window > 0 ? max(0, ctx - q_len - P.window + 1) : 0;
-        const int tiles_all = (ctx - 1 - (lo / BN) * BN) / BN + 1;
+        const int tiles_all = tile_range(lo, ctx - 1, P.keep, BN).tiles_all;
         if (threadIdx.x == 0) parts_here = min(P.n_split, (tiles_all + per - 1) / per);
     }
     __syncthreads();
@@ -622,7 +657,8 @@ __global__ void attention_merge_kernel(const Params P) {
             for (int j = 0; j < 8; ++j)
                 if (s0 + j < n_parts) acc += weight[s0 + j] * o[j];
         }
-        P.out[unit * HD + d] = __float2bfloat16_rn(wsum > 0.f ? acc / wsum : 0.f);
+        P.out[(size_t)t * P.out_stride + (size_t)h * HD + d] =
+            __float2bfloat16_rn(wsum > 0.f ? acc / wsum : 0.f);
     }
 }
 
@@ -1444,10 +1480,16 @@ MLS_API int mls_attention_mma(const void* qkv, void* out, const void* k_pool, co
                               int block_size, float scale, int window, float softcap, int n_tiles,
                               int n_small, int n_split, float* part_o, float* part_lse,
                               long long pool_pages, int* status, int use_tma,
-                              const float* sink, cudaStream_t stream) {
+                              const float* sink, const float* slopes, int keep_first,
+                              long long out_stride, cudaStream_t stream) {
     if (n_tokens <= 0 || n_req <= 0) return 0;
     if (n_heads % n_kv || n_split < 1 || n_split > MAX_SPLITS ||
         (n_split > 1 && (!part_o || !part_lse)))
+        return MLS_ERR_UNSUPPORTED;
+    if (out_stride <= 0) out_stride = (long long)n_heads * HD;
+    // slopes, kept first keys and rows inside a wider buffer: the kernels without TMA only
+    const bool plain = !slopes && keep_first <= 0 && out_stride == (long long)n_heads * HD;
+    if (!plain && (use_tma || (softcap > 0.f && slopes) || (out_stride & 1)))
         return MLS_ERR_UNSUPPORTED;
     static bool configured = false;
     if (!configured) {
@@ -1486,6 +1528,9 @@ MLS_API int mls_attention_mma(const void* qkv, void* out, const void* k_pool, co
     P.status = status;
     P.n_pages = pool_pages;
     P.sink = sink;
+    P.slopes = slopes;
+    P.keep = (window > 0 && keep_first > 0) ? keep_first : 0;
+    P.out_stride = out_stride;
     const bool tma_ok = use_tma && (block_size == 8 || block_size == 16 || block_size == 32 ||
                                     block_size == 64) && (HD % 64 == 0);
     (void)tma_ok;
@@ -1605,6 +1650,9 @@ MLS_API int mls_attention_decode_fused(const float* parts, int n_parts, long lon
     P.status = status;
     P.n_pages = pool_pages;
     P.sink = nullptr;                    // the fused step serves mixers without sinks
+    P.slopes = nullptr;
+    P.keep = 0;
+    P.out_stride = (long long)n_heads * HD;
     Fused F;
     F.parts = parts;
     F.n_parts = n_parts;

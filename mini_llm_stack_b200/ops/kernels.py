@@ -525,7 +525,7 @@ class Ops:
             lib = self._load("attention", {"MLS_HEAD_DIM": int(hd)})
             fn = _decl(lib, "mls_attention_mma",
                        [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _F, _I, _I, _I,
-                        _P, _P, _LL, _P, _I, _P, _P])
+                        _P, _P, _LL, _P, _I, _P, _P, _I, _LL, _P])
             tc = _decl(lib, "mls_attention_tc",
                        [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _F, _I, _I, _I, _LL,
                         _P, _P, _P])
@@ -584,9 +584,9 @@ class Ops:
         """Attention of the step's tokens over the pages.  ``slopes`` (float32 [n_heads]): the
         score of head h loses ``slopes[h] * (position - key's position)``.  ``keep_first``: a
         window does not hide the sequence's first so many keys.  ``out`` may be a block of
-        columns of a wider buffer.  The tensor-core kernels take none of the three: such a call
-        (or one with ``simt``, from a mixer that planned for it) runs on the one-warp-per-row
-        kernel.  ``softcap`` c > 0: scores become
+        columns of a wider buffer.  Of the tensor-core kernels the ``mma.sync`` ones without TMA
+        take these three, so a bfloat16 call with any of them runs there; ``simt`` sends the call
+        to the one-warp-per-row kernel.  ``softcap`` c > 0: scores become
         ``c * tanh(score / c)`` before the softmax.  ``sink`` (float32 [n_heads]): the softmax's
         denominator of head h also holds ``exp(sink[h])``, a term without key or value.  ``plan`` (the mixer's, from
         ``attention_facts``): ``n_tiles`` / ``n_tiles_tc`` / ``n_tiles_tc_wide`` tiles of the
@@ -598,18 +598,20 @@ class Ops:
         _need(slopes is None or (slopes.dtype == torch.float32 and slopes.shape == (n_heads,)
                                  and slopes.is_contiguous()), "attention: slopes are float32 [heads]")
         keep_first = int(keep_first or 0) if window else 0
-        plain = (slopes is None and keep_first == 0 and out.stride(0) == n_heads * hd
-                 and not simt)
+        plain = slopes is None and keep_first == 0 and out.stride(0) == n_heads * hd
+        _need(plain or not (softcap and slopes is not None),
+              "attention: a cap on the scores and slopes together are not supported")
         _need(sink is None or (sink.dtype == torch.float32 and sink.shape == (n_heads,)
                                and sink.is_contiguous()), "attention: sinks are float32 [heads]")
-        if self.attention_tensor_cores(hd) and qkv.dtype == torch.bfloat16 and plain:
+        if (self.attention_tensor_cores(hd) and qkv.dtype == torch.bfloat16 and not simt
+                and out.stride(0) % 2 == 0):
             fns = self._attention_libs.get(hd)
             _need(fns is not None, f"attention kernels for head size {hd} were not required")
             fn, tc = fns
             _need(plan is not None, "attention: the tensor-core kernels need the mixer's plan")
             n_tiles, n_small, n_split, n_tiles_tc = (plan.n_tiles, 1 if plan.any_small else 0,
                                                      plan.n_split, plan.n_tiles_tc)
-            if (n_tiles and hd in (64, 128) and g.block_size in (8, 16, 32, 64)
+            if (n_tiles and plain and hd in (64, 128) and g.block_size in (8, 16, 32, 64)
                     and self.attention_impl == "auto"):
                 # prompts and portions: the tcgen05 kernel; what is left for the call
                 # below are the requests of a few rows
@@ -628,7 +630,7 @@ class Ops:
                 scratch = self.scratch("attention_partials", n_split * units * (hd + 1))
                 part_o = scratch[:n_split * units * hd]
                 part_lse = scratch[n_split * units * hd:]
-            tma = (self.attention_impl != "no_tma" and hd % 64 == 0
+            tma = (self.attention_impl != "no_tma" and plain and hd % 64 == 0
                    and g.block_size in (8, 16, 32, 64))
             self.launches += (1 if n_tiles else 0) + (n_small and self._split_launches(
                 n_split, tma, step.n_requests * n_kv * n_split))
@@ -637,7 +639,8 @@ class Ops:
                       step.n_requests, t, n_heads, n_kv, g.block_size, float(scale), int(window),
                       float(softcap), n_tiles, n_small, n_split, _ptr(part_o), _ptr(part_lse),
                       cache.k_pool.shape[1], _ptr(self.status),
-                      0 if self.attention_impl == "no_tma" else 1, _ptr(sink), self._stream()),
+                      0 if (self.attention_impl == "no_tma" or not plain) else 1, _ptr(sink),
+                      _ptr(slopes), keep_first, out.stride(0), self._stream()),
                    "attention_mma")
             return
         self.launches += 1

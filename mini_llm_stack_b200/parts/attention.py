@@ -309,10 +309,7 @@ class UnrotatedAttention(Mixer):
         ops.require_part("headprep")
         if self.gate:
             ops.require_part("latent")               # the gate's kernel lives there
-        # the tensor-core kernels take neither slopes, kept first keys nor rows inside a wider
-        # buffer: such a mixer runs on the one-warp-per-row kernel and needs no plan
-        self._tensor_cores = (ops.attention_tensor_cores(self.pad_dim) and self.slopes is None
-                              and not self.keep_first and self.project)
+        self._tensor_cores = ops.attention_tensor_cores(self.pad_dim)
         if self._tensor_cores:
             ops.require_attention(self.pad_dim, self.n_heads, self.n_kv_heads)
         self._facts = ops.attention_facts(self.pad_dim)

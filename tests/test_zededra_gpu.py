@@ -200,9 +200,10 @@ def test_router_picks_lowest_index_on_ties_and_can_renormalise(rt32):
     idx = torch.empty(6, dtype=torch.int32, device="cuda")
     wt = torch.empty(6, device="cuda")
     for renorm in (0, 1):
-        # sigmoid scores, no correction, nothing added to the sum of the chosen scores
-        fns["topk"](z.data_ptr(), 2, 5, 3, renorm, 0, None, 0.0, idx.data_ptr(), wt.data_ptr(),
-                    rt32.ops._stream())
+        # rows of five logits; sigmoid scores, no correction, nothing added to the sum of the
+        # chosen scores, one group
+        fns["topk"](z.data_ptr(), 5, 2, 5, 3, renorm, 0, None, 0.0, 1, 1, idx.data_ptr(),
+                    wt.data_ptr(), rt32.ops._stream())
         assert idx.tolist() == [1, 2, 4, 0, 3, 4]
         want = torch.sigmoid(torch.tensor([[2.0, 2.0, 2.0], [3.0, 3.0, 1.0]]))
         if renorm:
