@@ -1,4 +1,4 @@
-"""``bench.py --design zededra | logulix | zefenex``: prefill and decode throughput of the design's
+"""``bench.py --design zededra | logulix | zefenex | movazen``: prefill and decode throughput of the design's
 layers at sizes that resemble a real model's, beside the dense Llama-style decoder at equal
 size.
 
@@ -95,13 +95,47 @@ def zefenex_config(s: dict, kind: str, layers: int, vocab: int = 32000) -> dict:
             "embedding": {"scale": 1.0}, "logit_softcap": 30.0, "layers": stack}
 
 
+def movazen_config(s: dict, kind: str, layers: int, vocab: int = 32000) -> dict:
+    """Layers of Movazen's mixers with its routed experts (sigmoid scores, a correction, eight
+    groups of which four are kept, clamped units, a gated shared expert) and its side input of
+    256 entries a layer: windowed attention with the dense decoder's heads (a window of 1,024
+    behind four kept tokens, per-head norms, slopes, the output gate), or softmax attention of
+    the same heads beside lightning attention of as many heads with keys and values of the
+    head size; ``mixers_only`` alternates the two without feed-forwards."""
+    kv = max(1, s["kv_rank"] // (2 * s["dim"]), s["heads"] // 16)
+    heads, dim = s["heads"], s["dim"]
+    attention = {"type": "attention",
+                 "mixer": {"dim": dim, "heads": heads, "kv_heads": kv, "vdim": dim,
+                           "scale": dim ** -0.5, "mask": {"size": 1024, "keep_first": 4}}}
+    parallel = {"type": "parallel",
+                "mixer": {"left": {"dim": dim, "heads": heads, "kv_heads": kv, "vdim": dim,
+                                   "scale": dim ** -0.5, "q_temp": {"coef": 0.1, "every": 512}},
+                          "left_scale": 0.6,
+                          "right": {"dim": dim, "heads": heads, "vdim": dim,
+                                    "decay": [1.0 - 2.0 ** (-5 - 3 * i / heads)
+                                              for i in range(heads)]},
+                          "right_scale": 0.5}}
+    moe = {"expert": {"ff": s["eff"], "limit": 7.0}, "kind": "moe",
+           "router": {"experts": s["experts"], "top": s["top"], "groups": {"count": 8, "keep": 4}},
+           "shared": {"ff": s["shared"], "limit": 7.0}}
+    if kind == "mixers_only":
+        stack = [dict(attention if i % 2 == 0 else parallel, mlp=None) for i in range(layers)]
+    else:
+        stack = [dict(attention if kind == "attention_moe" else parallel, mlp=moe)] * layers
+    return {"architecture": "Movazen", "vocab": vocab, "width": s["width"], "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0}, "token_side": {"dim": 256}, "layers": stack}
+
+
 DESIGNS = {
     "zededra": (zededra_config, ("latent_dense", "latent_moe", "mlstm_dense")),
     "logulix": (logulix_config, ("attention_dense", "wkv_dense", "retention_dense")),
     "zefenex": (zefenex_config, ("latent_dense", "latent_moe", "shared_cache_dense")),
+    "movazen": (movazen_config, ("attention_moe", "parallel_moe", "mixers_only")),
 }
 # rows of another design measured beside a design's own: the closest existing layers
-BESIDE = {"zefenex": (("zededra", "latent_dense"), ("zededra", "latent_moe"))}
+BESIDE = {"zefenex": (("zededra", "latent_dense"), ("zededra", "latent_moe")),
+          "movazen": (("zefenex", "latent_moe"), ("logulix", "attention_dense"),
+                      ("logulix", "retention_dense"))}
 
 
 def llama_config(s: dict, layers: int, vocab: int = 32000) -> dict:
@@ -120,7 +154,8 @@ _LEAVES = ("embed", "add_rmsnorm", "gather_add_rmsnorm", "add_layernorm", "resid
            "expert_glu", "expert_down", "expert_combine", "qk_conv_norm_rope_store",
            "tail_update", "token_shift_mix", "linear_scan", "scan_finish", "rotate_rows",
            "decay_lowrank", "relu_squared", "scale_", "settle_concat", "add_tanh_norm",
-           "latent_rope_prep", "sigmoid_gate", "softcap_")
+           "latent_rope_prep", "sigmoid_gate", "softcap_", "head_prep_store", "settle_cast",
+           "gelu_gate_rows", "rms_scale", "scan_finish_row")
 _PRODUCTS = ("linear", "linear_parts", "linear_swiglu", "linear_clamped_glu",
              "linear_relu_squared")
 

@@ -369,7 +369,7 @@ def main() -> int:
     ap.add_argument("--workload", default="decode", choices=["decode", "mixed_1b", "poisson_7b"],
                     help="decode: the contract's line; the others serve a request mix through "
                          "the scheduler and print their own line")
-    ap.add_argument("--design", default=None, choices=["zededra", "logulix", "zefenex"],
+    ap.add_argument("--design", default=None, choices=["zededra", "logulix", "zefenex", "movazen"],
                     help="instead of the default line: layers of this design at sizes that "
                          "resemble a real model's, beside the dense decoder at equal size "
                          "(prefill and decode tokens/s and the time of every kind of kernel)")

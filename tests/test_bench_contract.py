@@ -50,3 +50,12 @@ def test_design_option_builds_layers_of_equal_size():
         att = mod.logulix_config(s, "attention_dense", 2)["layers"][0]["mixer"]
         assert (att["heads"], att["kv_heads"], att["dim"]) == (dense.n_heads, dense.n_kv_heads,
                                                                dense.head_dim)
+        for kind in mod.DESIGNS["movazen"][1]:
+            m = config_from_dict(mod.movazen_config(s, kind, 2))
+            assert m.width == dense.d_model and len(m.layers) == dense.n_layers
+        att = mod.movazen_config(s, "attention_moe", 2)["layers"][0]["mixer"]
+        assert (att["heads"], att["kv_heads"], att["dim"]) == (dense.n_heads, dense.n_kv_heads,
+                                                               dense.head_dim)
+        moe = mod.movazen_config(s, "parallel_moe", 2)["layers"][0]["mlp"]
+        assert (moe["router"]["experts"], moe["router"]["top"], moe["expert"]["ff"]) == \
+            (s["experts"], s["top"], s["eff"])
