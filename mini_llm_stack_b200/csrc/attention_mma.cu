@@ -59,7 +59,7 @@ struct Params {
     long long n_pages;                   // pages of the pool: [Hkv, pages, block, HD]
     const float* sink;                   // [H] or nullptr: exp(sink_h) joins the softmax's
                                          // denominator, a term without key or value
-    // (the three below: the kernels without TMA only; the others get none of them)
+    // (slopes and kept keys: the kernels without TMA only; the others get neither)
     const float* slopes;                 // [H] or nullptr: the score of head h loses
                                          // slopes[h] * (query position - key position)
     int keep;                            // with a window: the first so many keys stay visible
@@ -1117,7 +1117,8 @@ attention_split_tma_kernel(const Params P, const Fused F,
         const float val = l > 0.f ? acc / l : 0.f;
         const size_t unit = (size_t)(tok0 + i) * P.n_heads + (kvh * P.group + g);
         if (P.n_split == 1) {
-            P.out[unit * HD + d] = __float2bfloat16_rn(val);
+            P.out[(size_t)(tok0 + i) * P.out_stride + (size_t)(kvh * P.group + g) * HD + d] =
+                __float2bfloat16_rn(val);
         } else if (P.cluster_merge) {
             // this CTA's result stays in its shared memory for the merge inside the cluster
             o_s[(size_t)4 * 16 * HD + idx] = val;
@@ -1165,8 +1166,8 @@ attention_split_tma_kernel(const Params P, const Fused F,
             }
             const int i = row / P.group, g = row - i * P.group;
             wsum += sink_term(P, kvh * P.group + g, m);
-            const size_t unit = (size_t)(tok0 + i) * P.n_heads + (kvh * P.group + g);
-            P.out[unit * HD + d] = __float2bfloat16_rn(wsum > 0.f ? acc / wsum : 0.f);
+            P.out[(size_t)(tok0 + i) * P.out_stride + (size_t)(kvh * P.group + g) * HD + d] =
+                __float2bfloat16_rn(wsum > 0.f ? acc / wsum : 0.f);
         }
         cluster_sync_all();              // nobody's shared memory goes away while it is read
     }
@@ -1388,7 +1389,7 @@ attention_tile_tma_kernel(const Params P, const __grid_constant__ CUtensorMap km
         const int row = half ? rB : rA;
         if (row >= rows) continue;
         const int i = row / P.group, g = row - i * P.group;
-        __nv_bfloat16* dst = P.out + (size_t)(tok0 + i) * P.n_heads * HD +
+        __nv_bfloat16* dst = P.out + (size_t)(tok0 + i) * P.out_stride +
                              (size_t)(kvh * P.group + g) * HD + (lane & 3) * 2;
         const float inv = half ? invB : invA;
 #pragma unroll
@@ -1487,9 +1488,9 @@ MLS_API int mls_attention_mma(const void* qkv, void* out, const void* k_pool, co
         (n_split > 1 && (!part_o || !part_lse)))
         return MLS_ERR_UNSUPPORTED;
     if (out_stride <= 0) out_stride = (long long)n_heads * HD;
-    // slopes, kept first keys and rows inside a wider buffer: the kernels without TMA only
-    const bool plain = !slopes && keep_first <= 0 && out_stride == (long long)n_heads * HD;
-    if (!plain && (use_tma || (softcap > 0.f && slopes) || (out_stride & 1)))
+    // slopes and kept first keys: the kernels without TMA only
+    const bool plain = !slopes && keep_first <= 0;
+    if ((!plain && (use_tma || (softcap > 0.f && slopes))) || (out_stride & 1))
         return MLS_ERR_UNSUPPORTED;
     static bool configured = false;
     if (!configured) {

@@ -79,6 +79,8 @@ struct Params {
     long long n_pages;                   // pages of the pool: [Hkv, pages, block, HD]
     const float* sink;                   // [H] or nullptr: exp(sink_h) joins the softmax's
                                          // denominator, a term without key or value
+    long long out_stride;                // elements between two tokens' rows of `out` (a multiple
+                                         // of eight: the rows are stored 16 bytes at a time)
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -456,7 +458,7 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
             if (P.sink && live && m_used != -INFINITY)
                 l += exp2f(P.sink[kvh * P.group + g] * LOG2E - m_used);
             const float inv = l > 0.f ? 1.0f / l : 0.f;
-            __nv_bfloat16* dst = P.out + (size_t)(tok0 + ti) * P.n_heads * HD +
+            __nv_bfloat16* dst = P.out + (size_t)(tok0 + ti) * P.out_stride +
                                  (size_t)(kvh * P.group + g) * HD;
 #pragma unroll
             for (int c0 = 0; c0 < HD; c0 += 32) {
@@ -498,7 +500,7 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
             const bool second = n_steps[1] > 0;            // else its accumulator was never written
             constexpr int HO = HD / 2;
             const uint32_t o0 = tmem + lane_base + COL_O + c * HO, o1 = o0 + BN;
-            __nv_bfloat16* dst = P.out + (size_t)(tok0 + ti) * P.n_heads * HD +
+            __nv_bfloat16* dst = P.out + (size_t)(tok0 + ti) * P.out_stride +
                                  (size_t)(kvh * P.group + g) * HD + c * HO;
 #pragma unroll
             for (int c0 = 0; c0 < HO; c0 += 16) {
@@ -589,7 +591,7 @@ MLS_API int mls_attention_tc(const void* qkv, void* out, const void* k_pool, con
                              const int* ctx_len, int n_req, int n_heads, int n_kv, int block_size,
                              float scale, int window, float softcap, int n_tiles, int n_tiles_wide,
                              int skip_small, long long pool_pages, int* status,
-                             const float* sink, cudaStream_t stream) {
+                             const float* sink, long long out_stride, cudaStream_t stream) {
 #if MLS_HEAD_DIM == 64 || MLS_HEAD_DIM == 128
     if (n_tiles <= 0 || n_req <= 0) return 0;
     if (n_heads % n_kv) return MLS_ERR_UNSUPPORTED;
@@ -630,6 +632,8 @@ MLS_API int mls_attention_tc(const void* qkv, void* out, const void* k_pool, con
     P.status = status;
     P.n_pages = pool_pages;
     P.sink = sink;
+    P.out_stride = out_stride > 0 ? out_stride : (long long)n_heads * HD;
+    if (P.out_stride % 8) return MLS_ERR_UNSUPPORTED;
     MLS_LAUNCH((attention_tc_kernel), dim3(n_kv, P.two_tiles ? n_tiles_wide : n_tiles),
                dim3(THREADS), SMEM_BYTES, stream, P, kmap, vmap, kmap_wide, vmap_wide);
     return launch_status();

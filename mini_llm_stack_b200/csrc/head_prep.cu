@@ -18,10 +18,11 @@
 #include "page_tail.cuh"
 
 namespace {
-constexpr int HP_THREADS = 128;
+constexpr int HP_THREADS = 128;      // a block of a prompt's token
+constexpr int HP_MAX_THREADS = 512;  // few tokens: up to a warp a head, so that no warp takes many in turn
 
 template <typename T>
-__global__ void __launch_bounds__(HP_THREADS)
+__global__ void __launch_bounds__(HP_MAX_THREADS)
 head_prep_kernel(const float* __restrict__ proj, int proj_width, int q_col, int k_col, int v_col,
                  const float* __restrict__ b_q, const float* __restrict__ b_k,
                  const float* __restrict__ b_v, const float* __restrict__ w_q,
@@ -103,14 +104,17 @@ MLS_API int mls_head_prep_store(const float* proj, int proj_width, int q_col, in
                                 int writes, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (e <= 0 || f <= 0 || hd < e || hd < f || n_heads <= 0 || n_kv <= 0) return MLS_ERR_UNSUPPORTED;
+    const int units = n_heads + (writes ? 2 * n_kv : 0);
+    const int threads = n_tokens > 64 ? HP_THREADS
+        : (32 * units < HP_THREADS ? HP_THREADS : (32 * units > HP_MAX_THREADS ? HP_MAX_THREADS : 32 * units));
     if (dtype == MLS_BF16)
-        MLS_LAUNCH((head_prep_kernel<__nv_bfloat16>), dim3(n_tokens), dim3(HP_THREADS), 0, stream,
+        MLS_LAUNCH((head_prep_kernel<__nv_bfloat16>), dim3(n_tokens), dim3(threads), 0, stream,
                    proj, proj_width, q_col, k_col, v_col, b_q, b_k, b_v, w_q, w_k, eps, temp_coef,
                    temp_every, v_scale, positions, slot_map, (__nv_bfloat16*)q_out, q_width,
                    (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, block_size, n_pages, n_tokens,
                    n_heads, n_kv, e, f, hd, writes, status);
     else
-        MLS_LAUNCH((head_prep_kernel<float>), dim3(n_tokens), dim3(HP_THREADS), 0, stream, proj,
+        MLS_LAUNCH((head_prep_kernel<float>), dim3(n_tokens), dim3(threads), 0, stream, proj,
                    proj_width, q_col, k_col, v_col, b_q, b_k, b_v, w_q, w_k, eps, temp_coef,
                    temp_every, v_scale, positions, slot_map, (float*)q_out, q_width,
                    (float*)k_pool, (float*)v_pool, block_size, n_pages, n_tokens, n_heads, n_kv,

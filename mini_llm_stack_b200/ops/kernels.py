@@ -528,7 +528,7 @@ class Ops:
                         _P, _P, _LL, _P, _I, _P, _P, _I, _LL, _P])
             tc = _decl(lib, "mls_attention_tc",
                        [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _F, _I, _I, _I, _LL,
-                        _P, _P, _P])
+                        _P, _P, _LL, _P])
             fused = _decl(lib, "mls_attention_decode_fused",
                           [_P, _I, _LL, _P, _P, _P, _I, _P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I,
                            _I, _I, _F, _I, _I, _P, _P, _LL, _P, _P])
@@ -585,8 +585,9 @@ class Ops:
         score of head h loses ``slopes[h] * (position - key's position)``.  ``keep_first``: a
         window does not hide the sequence's first so many keys.  ``out`` may be a block of
         columns of a wider buffer.  Of the tensor-core kernels the ``mma.sync`` ones without TMA
-        take these three, so a bfloat16 call with any of them runs there; ``simt`` sends the call
-        to the one-warp-per-row kernel.  ``softcap`` c > 0: scores become
+        take the first two, so a bfloat16 call with either runs there (rows of a wider buffer are
+        taken by all of them, 16 bytes apart for those with TMA); ``simt`` sends the call to the
+        one-warp-per-row kernel.  ``softcap`` c > 0: scores become
         ``c * tanh(score / c)`` before the softmax.  ``sink`` (float32 [n_heads]): the softmax's
         denominator of head h also holds ``exp(sink[h])``, a term without key or value.  ``plan`` (the mixer's, from
         ``attention_facts``): ``n_tiles`` / ``n_tiles_tc`` / ``n_tiles_tc_wide`` tiles of the
@@ -598,7 +599,7 @@ class Ops:
         _need(slopes is None or (slopes.dtype == torch.float32 and slopes.shape == (n_heads,)
                                  and slopes.is_contiguous()), "attention: slopes are float32 [heads]")
         keep_first = int(keep_first or 0) if window else 0
-        plain = slopes is None and keep_first == 0 and out.stride(0) == n_heads * hd
+        plain = slopes is None and keep_first == 0 and out.stride(0) % 8 == 0
         _need(plain or not (softcap and slopes is not None),
               "attention: a cap on the scores and slopes together are not supported")
         _need(sink is None or (sink.dtype == torch.float32 and sink.shape == (n_heads,)
@@ -620,7 +621,8 @@ class Ops:
                           _ptr(g.block_table), g.max_blocks, _ptr(step.cu_q), _ptr(step.ctx_len),
                           step.n_requests, n_heads, n_kv, g.block_size, float(scale), int(window),
                           float(softcap), n_tiles_tc, plan.n_tiles_tc_wide, n_small, cache.k_pool.shape[1],
-                          _ptr(self.status), _ptr(sink), self._stream()), "attention_tc")
+                          _ptr(self.status), _ptr(sink), out.stride(0), self._stream()),
+                       "attention_tc")
                 n_tiles = 0
                 if not n_small:
                     return
