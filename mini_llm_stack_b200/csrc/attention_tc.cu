@@ -81,6 +81,10 @@ struct Params {
                                          // denominator, a term without key or value
     long long out_stride;                // elements between two tokens' rows of `out` (a multiple
                                          // of eight: the rows are stored 16 bytes at a time)
+    const float* slopes;                 // [H] or nullptr: the score of head h loses
+                                         // slopes[h] * (query position - key position)
+    float inv_scale;                     // 1 / scale: the bias joins the scores in raw units
+    int keep;                            // with a window: the first so many keys stay visible
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -141,13 +145,18 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
     const int lo = P.window > 0 ? max(0, pos0 + i_first - P.window + 1) : 0;
     const int* table = P.block_table + (size_t)r * P.max_blocks;
     const int kbase0 = (lo / BN) * BN;
-    const int n_tiles = (hi - kbase0) / BN + 1;
+    // with kept first keys: first the tiles of kept keys that lie wholly before the window's
+    // first tile, then the tiles from the window's on (kept keys inside those pass the masks)
+    const int keep_tiles = (P.keep > 0 && lo > 0)
+        ? min((min(P.keep, lo) + BN - 1) / BN, kbase0 / BN) : 0;
+    const int n_tiles = keep_tiles + (hi - kbase0) / BN + 1;
+    auto tile_base = [&](int t) { return t < keep_tiles ? t * BN : kbase0 + (t - keep_tiles) * BN; };
     // steps of each chain, and the key tile of chain c's step i
     int n_steps[2];
     if (P.two_tiles) {
         // chain 0's rows end earlier: it may need a key tile less; chain 1 may have no rows
         const int last0 = (min(rows, row0 + CHAIN_ROWS) - 1) / P.group;
-        n_steps[0] = (pos0 + last0 - kbase0) / BN + 1;
+        n_steps[0] = keep_tiles + (pos0 + last0 - kbase0) / BN + 1;
         n_steps[1] = row0 + CHAIN_ROWS < rows ? n_tiles : 0;
     } else {
         n_steps[0] = (n_tiles + 1) / 2;
@@ -215,13 +224,13 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
             const uint32_t full = bar((which ? B_V_FULL : B_K_FULL) + slot);
             const uint32_t empty = bar((which ? B_V_EMPTY : B_K_EMPTY) + slot);
             if (!mbar_wait(empty, ((t / stages) & 1) ^ 1)) return false;
-            const int kb = kbase0 + t * BN;
+            const int kb = tile_base(t);
             const uint32_t stage = which ? v_smem + slot * V_STAGE : k_smem + slot * K_STAGE;
             bool valid = false;
             int page = -1;
             if (lane < ppt) {
                 const int j0 = kb + lane * bs;
-                if (j0 <= hi && j0 + bs > lo) {
+                if (j0 <= hi && (j0 + bs > lo || j0 < P.keep)) {
                     page = table[j0 / bs];
                     valid = page >= 0;
                 }
@@ -331,6 +340,7 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
         const int c = chain;
         const int pos = live ? pos0 + ti : -1;
         const int lo_row = P.window > 0 ? pos - P.window + 1 : 0;
+        const float slope_raw = (P.slopes && live) ? P.slopes[kvh * P.group + g] * P.inv_scale : 0.f;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
         const uint32_t s_addr = tmem + lane_base + COL_S + c * BN;
         const uint32_t o_addr = tmem + lane_base + COL_O + c * BN;
@@ -354,7 +364,7 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
         float m_used = -INFINITY, l = 0.f;
         const int steps = n_steps[c];
         for (int i = 0; i < steps && !timed_out; ++i) {
-            const int kbase = kbase0 + key_tile(c, i) * BN;
+            const int kbase = tile_base(key_tile(c, i));
             if (!mbar_wait(bar(B_S_FULL + c), i & 1)) {
                 timed_out = true;
                 break;
@@ -381,12 +391,18 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
                     sc[e] = P.cap_over_scale * (1.0f - __fdividef(2.0f, 1.0f + ex));
                 }
             }
+            if (P.slopes) {
+                // the distance to the key times the head's slope, in the scores' raw units
+                const float d0 = (float)(pos - kbase) * slope_raw;
+#pragma unroll
+                for (int e = 0; e < BN; ++e) sc[e] -= fmaf(-(float)e, slope_raw, d0);
+            }
             const bool masked = kbase + BN - 1 > pos || kbase < lo_row;
             if (__any_sync(0xffffffffu, masked)) {
 #pragma unroll
                 for (int e = 0; e < BN; ++e) {
                     const int jj = kbase + e;
-                    if (jj > pos || jj < lo_row) sc[e] = -INFINITY;
+                    if (jj > pos || (jj < lo_row && jj >= P.keep)) sc[e] = -INFINITY;
                 }
             }
             // eight running maxima, then their maximum: no chain of dependent steps
@@ -591,7 +607,8 @@ MLS_API int mls_attention_tc(const void* qkv, void* out, const void* k_pool, con
                              const int* ctx_len, int n_req, int n_heads, int n_kv, int block_size,
                              float scale, int window, float softcap, int n_tiles, int n_tiles_wide,
                              int skip_small, long long pool_pages, int* status,
-                             const float* sink, long long out_stride, cudaStream_t stream) {
+                             const float* sink, long long out_stride, const float* slopes,
+                             int keep_first, cudaStream_t stream) {
 #if MLS_HEAD_DIM == 64 || MLS_HEAD_DIM == 128
     if (n_tiles <= 0 || n_req <= 0) return 0;
     if (n_heads % n_kv) return MLS_ERR_UNSUPPORTED;
@@ -633,7 +650,10 @@ MLS_API int mls_attention_tc(const void* qkv, void* out, const void* k_pool, con
     P.n_pages = pool_pages;
     P.sink = sink;
     P.out_stride = out_stride > 0 ? out_stride : (long long)n_heads * HD;
-    if (P.out_stride % 8) return MLS_ERR_UNSUPPORTED;
+    if (P.out_stride % 8 || (slopes && softcap > 0.f)) return MLS_ERR_UNSUPPORTED;
+    P.slopes = slopes;
+    P.inv_scale = 1.0f / scale;
+    P.keep = (window > 0 && keep_first > 0) ? keep_first : 0;
     MLS_LAUNCH((attention_tc_kernel), dim3(n_kv, P.two_tiles ? n_tiles_wide : n_tiles),
                dim3(THREADS), SMEM_BYTES, stream, P, kmap, vmap, kmap_wide, vmap_wide);
     return launch_status();

@@ -528,7 +528,7 @@ class Ops:
                         _P, _P, _LL, _P, _I, _P, _P, _I, _LL, _P])
             tc = _decl(lib, "mls_attention_tc",
                        [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _F, _I, _I, _I, _LL,
-                        _P, _P, _LL, _P])
+                        _P, _P, _LL, _P, _I, _P])
             fused = _decl(lib, "mls_attention_decode_fused",
                           [_P, _I, _LL, _P, _P, _P, _I, _P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I,
                            _I, _I, _F, _I, _I, _P, _P, _LL, _P, _P])
@@ -584,10 +584,10 @@ class Ops:
         """Attention of the step's tokens over the pages.  ``slopes`` (float32 [n_heads]): the
         score of head h loses ``slopes[h] * (position - key's position)``.  ``keep_first``: a
         window does not hide the sequence's first so many keys.  ``out`` may be a block of
-        columns of a wider buffer.  Of the tensor-core kernels the ``mma.sync`` ones without TMA
-        take the first two, so a bfloat16 call with either runs there (rows of a wider buffer are
-        taken by all of them, 16 bytes apart for those with TMA); ``simt`` sends the call to the
-        one-warp-per-row kernel.  ``softcap`` c > 0: scores become
+        columns of a wider buffer.  Of the tensor-core kernels the tcgen05 kernel (prompts) and
+        the ``mma.sync`` ones without TMA take the first two, so a bfloat16 call with either runs
+        there (rows of a wider buffer are taken by all of them, 16 bytes apart for those with
+        TMA); ``simt`` sends the call to the one-warp-per-row kernel.  ``softcap`` c > 0: scores become
         ``c * tanh(score / c)`` before the softmax.  ``sink`` (float32 [n_heads]): the softmax's
         denominator of head h also holds ``exp(sink[h])``, a term without key or value.  ``plan`` (the mixer's, from
         ``attention_facts``): ``n_tiles`` / ``n_tiles_tc`` / ``n_tiles_tc_wide`` tiles of the
@@ -612,8 +612,8 @@ class Ops:
             _need(plan is not None, "attention: the tensor-core kernels need the mixer's plan")
             n_tiles, n_small, n_split, n_tiles_tc = (plan.n_tiles, 1 if plan.any_small else 0,
                                                      plan.n_split, plan.n_tiles_tc)
-            if (n_tiles and plain and hd in (64, 128) and g.block_size in (8, 16, 32, 64)
-                    and self.attention_impl == "auto"):
+            if (n_tiles and hd in (64, 128) and g.block_size in (8, 16, 32, 64)
+                    and self.attention_impl == "auto" and out.stride(0) % 8 == 0):
                 # prompts and portions: the tcgen05 kernel; what is left for the call
                 # below are the requests of a few rows
                 self.launches += 1
@@ -621,8 +621,8 @@ class Ops:
                           _ptr(g.block_table), g.max_blocks, _ptr(step.cu_q), _ptr(step.ctx_len),
                           step.n_requests, n_heads, n_kv, g.block_size, float(scale), int(window),
                           float(softcap), n_tiles_tc, plan.n_tiles_tc_wide, n_small, cache.k_pool.shape[1],
-                          _ptr(self.status), _ptr(sink), out.stride(0), self._stream()),
-                       "attention_tc")
+                          _ptr(self.status), _ptr(sink), out.stride(0), _ptr(slopes), keep_first,
+                          self._stream()), "attention_tc")
                 n_tiles = 0
                 if not n_small:
                     return

@@ -329,6 +329,23 @@ def test_far_keys_window_edges_and_kept_tokens(models, dtype):
         close(r.logits("a"), whole.logits("a").numpy(), dtype, "far keys")
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_prompts_walk_kept_tiles_and_window_tiles(models, dtype):
+    """Prompts long enough that the rows' window begins several key tiles behind the kept first
+    keys: whole, and cut where the second portion's first rows see the kept keys only through
+    their own tile."""
+    folder, cfg, w = models[("wide", dtype)]
+    tokens = {"a": tokens_for(cfg["vocab"], 330, 77), "b": tokens_for(cfg["vocab"], 330, 77)}
+    want = PM.forward(cfg, w, tokens["a"])
+    r = Replayer(folder, dtype, num_blocks=48)
+    r.step([("a", 330)], tokens, end=["a"])
+    close(r.logits("a"), want, dtype, "whole long prompt")
+    r.step([("b", 150)], tokens)
+    r.step([("b", 179)], tokens)
+    r.step([("b", 1)], tokens, end=["b"])
+    close(r.logits("b"), want, dtype, "long prompt in two portions")
+
+
 def test_long_decoding_through_graphs(models):
     folder, cfg, w = models[("wide", "bfloat16")]
     lens = {"a": 150, "b": 131}
