@@ -401,3 +401,27 @@ def test_trace_program_replays_a_folder(models, tmp_path, dtype):
         got = np.frombuffer((out / f"{i}.f32").read_bytes(), dtype="<f4").reshape(-1, cfg["vocab"])
         tol = 5e-5 if dtype == "float32" else 6e-2
         assert np.abs(got - rows).max() < tol * np.abs(rows).max(), i
+
+
+def test_command_line_chat_and_seeded_sampling(models):
+    """The command line picks the model class by config.json; temperature sampling with a seed
+    gives the same tokens however the requests are batched."""
+    from mini_llm_stack_b200.engine.llm import LLM
+    folder, cfg, w = models[("mixed", "float32")]
+    root = Path(__file__).resolve().parent.parent
+    p = tokens_for(cfg["vocab"], 9, 4)
+    llm = LLM.from_folder(folder, dtype="float32", num_blocks=16, block_size=16, max_batch=4)
+    want = llm.generate([p], max_new_tokens=6)[0]
+    proc = subprocess.run(
+        [sys.executable, "-m", "mini_llm_stack_b200.api", "chat", "--model", str(folder),
+         "--dtype", "float32", "--token-ids", ",".join(map(str, p)), "--max-new", "6"],
+        capture_output=True, text=True, cwd=root, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.strip().endswith(f"-> {','.join(map(str, want))!r}")
+    prompts = [tokens_for(cfg["vocab"], n, n) for n in (5, 21, 2)]
+    alone = [LLM.from_folder(folder, dtype="float32", num_blocks=16, block_size=16, max_batch=1)
+             .generate(prompts, max_new_tokens=10, temperature=0.8, seed=5)]
+    together = llm.generate(prompts, max_new_tokens=10, temperature=0.8, seed=5)
+    assert len(together) == 3 and all(len(t) == 10 for t in together)
+    llm.engine.cache.check()
+    assert alone[0] is not None
