@@ -100,6 +100,9 @@ __device__ __forceinline__ uint32_t swz(uint32_t tile, int row, int chunk) {
 }
 #define MLS_STATUS_BAD_SMEM 16       // dynamic shared memory is not 1024-byte aligned
 
+// EXTRA: slopes and kept first keys (an instantiation of its own, so that the kernel of the
+// models without them carries none of their arithmetic or registers).
+template <bool EXTRA>
 __global__ void __launch_bounds__(THREADS)
 attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
                     const __grid_constant__ CUtensorMap vmap,
@@ -147,8 +150,9 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
     const int kbase0 = (lo / BN) * BN;
     // with kept first keys: first the tiles of kept keys that lie wholly before the window's
     // first tile, then the tiles from the window's on (kept keys inside those pass the masks)
-    const int keep_tiles = (P.keep > 0 && lo > 0)
-        ? min((min(P.keep, lo) + BN - 1) / BN, kbase0 / BN) : 0;
+    const int keep = EXTRA ? P.keep : 0;
+    const int keep_tiles = (keep > 0 && lo > 0)
+        ? min((min(keep, lo) + BN - 1) / BN, kbase0 / BN) : 0;
     const int n_tiles = keep_tiles + (hi - kbase0) / BN + 1;
     auto tile_base = [&](int t) { return t < keep_tiles ? t * BN : kbase0 + (t - keep_tiles) * BN; };
     // steps of each chain, and the key tile of chain c's step i
@@ -230,7 +234,7 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
             int page = -1;
             if (lane < ppt) {
                 const int j0 = kb + lane * bs;
-                if (j0 <= hi && (j0 + bs > lo || j0 < P.keep)) {
+                if (j0 <= hi && (j0 + bs > lo || j0 < keep)) {
                     page = table[j0 / bs];
                     valid = page >= 0;
                 }
@@ -340,7 +344,8 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
         const int c = chain;
         const int pos = live ? pos0 + ti : -1;
         const int lo_row = P.window > 0 ? pos - P.window + 1 : 0;
-        const float slope_raw = (P.slopes && live) ? P.slopes[kvh * P.group + g] * P.inv_scale : 0.f;
+        const float slope_raw =
+            (EXTRA && P.slopes && live) ? P.slopes[kvh * P.group + g] * P.inv_scale : 0.f;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
         const uint32_t s_addr = tmem + lane_base + COL_S + c * BN;
         const uint32_t o_addr = tmem + lane_base + COL_O + c * BN;
@@ -391,7 +396,7 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
                     sc[e] = P.cap_over_scale * (1.0f - __fdividef(2.0f, 1.0f + ex));
                 }
             }
-            if (P.slopes) {
+            if (EXTRA && P.slopes) {
                 // the distance to the key times the head's slope, in the scores' raw units
                 const float d0 = (float)(pos - kbase) * slope_raw;
 #pragma unroll
@@ -402,7 +407,7 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
 #pragma unroll
                 for (int e = 0; e < BN; ++e) {
                     const int jj = kbase + e;
-                    if (jj > pos || (jj < lo_row && jj >= P.keep)) sc[e] = -INFINITY;
+                    if (jj > pos || (jj < lo_row && jj >= keep)) sc[e] = -INFINITY;
                 }
             }
             // eight running maxima, then their maximum: no chain of dependent steps
@@ -616,8 +621,11 @@ MLS_API int mls_attention_tc(const void* qkv, void* out, const void* k_pool, con
         return MLS_ERR_UNSUPPORTED;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel,
+        cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel<false>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(attention_tc_kernel<true>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
@@ -654,8 +662,12 @@ MLS_API int mls_attention_tc(const void* qkv, void* out, const void* k_pool, con
     P.slopes = slopes;
     P.inv_scale = 1.0f / scale;
     P.keep = (window > 0 && keep_first > 0) ? keep_first : 0;
-    MLS_LAUNCH((attention_tc_kernel), dim3(n_kv, P.two_tiles ? n_tiles_wide : n_tiles),
-               dim3(THREADS), SMEM_BYTES, stream, P, kmap, vmap, kmap_wide, vmap_wide);
+    if (P.slopes || P.keep > 0)
+        MLS_LAUNCH((attention_tc_kernel<true>), dim3(n_kv, P.two_tiles ? n_tiles_wide : n_tiles),
+                   dim3(THREADS), SMEM_BYTES, stream, P, kmap, vmap, kmap_wide, vmap_wide);
+    else
+        MLS_LAUNCH((attention_tc_kernel<false>), dim3(n_kv, P.two_tiles ? n_tiles_wide : n_tiles),
+                   dim3(THREADS), SMEM_BYTES, stream, P, kmap, vmap, kmap_wide, vmap_wide);
     return launch_status();
 #else
     return MLS_ERR_UNSUPPORTED;
