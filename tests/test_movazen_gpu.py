@@ -344,6 +344,17 @@ def test_long_prompts_walk_kept_tiles_and_window_tiles(models, dtype):
     r.step([("b", 179)], tokens)
     r.step([("b", 1)], tokens, end=["b"])
     close(r.logits("b"), want, dtype, "long prompt in two portions")
+    if dtype == "bfloat16":
+        # both ways in which the tcgen05 kernel forms its two chains of rows
+        ops = r.model.runtime.ops
+        for rows in (128, 256):
+            for hd in (64, 128):
+                ops.set_attention_rows(hd, rows)
+            tokens[f"w{rows}"] = tokens["a"]
+            r.step([(f"w{rows}", 330)], tokens, end=[f"w{rows}"])
+            close(r.logits(f"w{rows}"), want, dtype, f"whole long prompt, {rows} rows a CTA")
+        for hd in (64, 128):
+            ops.set_attention_rows(hd, 0)
 
 
 def test_long_decoding_through_graphs(models):
