@@ -110,11 +110,11 @@ def movazen_config(s: dict, kind: str, layers: int, vocab: int = 32000) -> dict:
     parallel = {"type": "parallel",
                 "mixer": {"left": {"dim": dim, "heads": heads, "kv_heads": kv, "vdim": dim,
                                    "scale": dim ** -0.5, "q_temp": {"coef": 0.1, "every": 512}},
-                          "left_scale": 0.6,
+                          "left_scale": 0.7,
                           "right": {"dim": dim, "heads": heads, "vdim": dim,
                                     "decay": [1.0 - 2.0 ** (-5 - 3 * i / heads)
                                               for i in range(heads)]},
-                          "right_scale": 0.5}}
+                          "right_scale": 0.4}}
     moe = {"expert": {"ff": s["eff"], "limit": 7.0}, "kind": "moe",
            "router": {"experts": s["experts"], "top": s["top"], "groups": {"count": 8, "keep": 4}},
            "shared": {"ff": s["shared"], "limit": 7.0}}

@@ -151,9 +151,11 @@ def clamped_unit(h, w, limit):
     return (g * sigmoid(GATE_ALPHA * g) * (u + 1.0)) @ w["down"].T
 
 
-def choose_experts(choice, top: int, groups=None):
+def choose_experts(choice, top: int, groups=None, margins=None):
     """Indices of the ``top`` largest choice scores (lowest index on a tie) among the
-    experts of the best groups: a group's score is the sum of its two largest choice scores."""
+    experts of the best groups: a group's score is the sum of its two largest choice scores.
+    ``margins`` (a list) receives the gap between the last kept and the first refused group's
+    score and the gap between the last chosen and the first refused expert's choice score."""
     choice = np.array(choice, dtype=np.float64)
     n = len(choice)
     allowed = np.ones(n, dtype=bool)
@@ -163,28 +165,33 @@ def choose_experts(choice, top: int, groups=None):
         for gi in range(groups["count"]):
             part = sorted(choice[gi * size:(gi + 1) * size], reverse=True)
             score.append(sum(part[:2]))
-        best = sorted(range(groups["count"]), key=lambda gi: (-score[gi], gi))[:groups["keep"]]
+        ranked = sorted(range(groups["count"]), key=lambda gi: (-score[gi], gi))
+        best = ranked[:groups["keep"]]
+        if margins is not None and len(ranked) > groups["keep"]:
+            margins.append(score[best[-1]] - score[ranked[groups["keep"]]])
         allowed[:] = False
         for gi in best:
             allowed[gi * size:(gi + 1) * size] = True
     order = sorted((i for i in range(n) if allowed[i]), key=lambda i: (-choice[i], i))
+    if margins is not None and len(order) > top:
+        margins.append(choice[order[top - 1]] - choice[order[top]])
     return order[:top]
 
 
 def routed_experts(h, w, mlp, margins=None):
     """Mixture of clamped units behind a sigmoid router with a correction for the choice,
     groups, renormalised weights and a gated shared expert.  ``margins`` (a list) collects,
-    per token, the gap between the last chosen and the first refused choice score."""
+    per token, the smallest gap by which a group or an expert was taken over the next one."""
     router = mlp["router"]
     n, top = router["experts"], router["top"]
     out = np.zeros_like(h)
     for i in range(h.shape[0]):
         s = sigmoid(w["router"] @ h[i])
         choice = s + w["correction"]
-        chosen = choose_experts(choice, top, router.get("groups"))
+        gaps = []
+        chosen = choose_experts(choice, top, router.get("groups"), gaps)
         if margins is not None:
-            rest = [choice[j] for j in range(n) if j not in chosen]
-            margins.append(min(choice[j] for j in chosen) - max(rest) if rest else np.inf)
+            margins.append(min(gaps) if gaps else np.inf)
         total = sum(s[j] for j in chosen) + RENORM_EPS
         for j in chosen:
             out[i] += (s[j] / total) * clamped_unit(h[i], sub(w, f"e{j}"), mlp["expert"]["limit"])
@@ -207,7 +214,7 @@ def sub(tensors: dict, prefix: str) -> dict:
     return {n[len(prefix) + 1:]: t for n, t in tensors.items() if n.startswith(prefix + ".")}
 
 
-def forward(config: dict, tensors: dict, tokens, want_layers: bool = False):
+def forward(config: dict, tensors: dict, tokens, want_layers: bool = False, margins=None):
     eps = config["norm"]["eps"]
     width = config["width"]
     scale = (config.get("embedding") or {}).get("scale", 1.0)
@@ -225,7 +232,7 @@ def forward(config: dict, tensors: dict, tokens, want_layers: bool = False):
             raise ValueError(layer["type"])
         if layer.get("mlp") is not None:
             h = model_norm(x, w["norm2"], eps)
-            x = x + routed_experts(h, sub(w, "mlp"), layer["mlp"])
+            x = x + routed_experts(h, sub(w, "mlp"), layer["mlp"], margins)
         if side is not None:
             x = x + token_side_input(x, tokens, sub(w, "side"), tensors["side.embed"], i,
                                      side["dim"], eps)

@@ -26,10 +26,12 @@ pytestmark = pytest.mark.gpu
 
 # largest |engine - plain| of a row as a fraction of the largest |logit|: float32 differs from
 # the float64 oracle by the order of its sums, bfloat16 by the rounding of products and
-# activations.  A router's close call may fall the other way in a bfloat16 run: a few rows of a
-# hundred may differ by more.
+# activations.  A router's close call could fall the other way in a bfloat16 run, so the models
+# of the bfloat16 runs have routers whose choices rest on their corrections (``decisive_routers``:
+# clear margins, the weights still follow the tokens); the float32 runs keep routers that choose
+# by the token.  A row in a hundred of a bfloat16 run may still differ by more.
 TOL = {"float32": 5e-5, "bfloat16": 4e-2}
-LOOSE_ROWS = {"float32": 0.0, "bfloat16": 0.04}
+LOOSE_ROWS = {"float32": 0.0, "bfloat16": 0.02}
 
 
 def close(got, want, dtype, what, tol=None):
@@ -65,7 +67,13 @@ def models(tmp_path_factory):
                             ("sharp_wide", M.M_WIDE, sharp(5.0))):
         for dtype in ("float32", "bfloat16"):
             folder = tmp / f"{key}_{dtype}"
-            cfg, w = M.make_movazen(folder, raw, 11, dtype, patch=patch)
+
+            def both(w, patch=patch, dtype=dtype, raw=raw):
+                if patch:
+                    patch(w)
+                if dtype == "bfloat16":
+                    M.decisive_routers(w, raw)
+            cfg, w = M.make_movazen(folder, raw, 11, dtype, patch=both)
             out[(key, dtype)] = (folder, cfg, w)
     return out
 
@@ -146,7 +154,7 @@ def test_head_preparation_kernel(rt32, act, options):
     assert kp[:, 1, :2].isnan().all() and kp[:, 2].isnan().all()
 
 
-@pytest.mark.parametrize("experts, top, groups", [(8, 3, (2, 1)), (12, 2, (4, 2)), (6, 6, (3, 3)),
+@pytest.mark.parametrize("experts, top, groups", [(10, 3, (2, 1)), (12, 2, (4, 2)), (6, 6, (3, 3)),
                                                   (5, 2, None), (8, 1, (8, 1)), (64, 4, (8, 3))])
 def test_grouped_routing_kernel(rt32, experts, top, groups):
     g = torch.Generator().manual_seed(experts)

@@ -86,9 +86,9 @@ M_WIDE = {
     "embedding": {"scale": 4.0}, "token_side": {"dim": 16},
     "layers": [
         layer(attention(4, 2, 64, 48, 0.125, window=70, keep_first=20),
-              moe(8, 3, 64, 1.5, groups=(2, 1), shared=(96, 1.0))),
-        layer(parallel((4, 2, 64, 64, 0.125, (0.3, 32)), (2, 32, 64, (0.9, 0.999)), 0.6, 0.5),
-              moe(4, 2, 32, 1.5)),
+              moe(8, 2, 64, 1.25, groups=(4, 2), shared=(80, 0.9))),
+        layer(parallel((4, 2, 64, 64, 0.11, (0.25, 32)), (2, 32, 64, (0.9, 0.995)), 0.7, 0.45),
+              moe(4, 2, 32, 2.5)),
         layer(attention(2, 1, 128, 128, 0.09, window=33, keep_first=1)),
     ],
 }
@@ -99,6 +99,30 @@ def one_layer(mixer_layer, mlp=None, width: int = 40, vocab: int = 61, eps: floa
     """A model of the embedding, one layer, the final norm and the head."""
     return dict({"architecture": "Movazen", "vocab": vocab, "width": width, "norm": {"eps": eps},
                  "layers": [layer(mixer_layer, mlp)]}, **top)
+
+
+def decisive_routers(w, raw: dict):
+    """Make every router's choice rest on its correction: an uneven ladder of corrections over
+    scores that barely move with the token, drawn again until every expert and every group's
+    score (the sum of its two largest) stands a fifth of a score or more from the next.  Groups
+    and experts are then taken by clear margins (no close call that a 16-bit rounding could
+    turn), while the weights of the chosen experts still follow the token's scores."""
+    for i, layer in enumerate(raw["layers"]):
+        mlp = layer.get("mlp")
+        if mlp is None:
+            continue
+        e = mlp["router"]["experts"]
+        count = (mlp["router"].get("groups") or {}).get("count", 1)
+        g = torch.Generator().manual_seed(100 + i)
+        while True:
+            c = 0.3 * torch.randperm(e, generator=g).double() + 0.1 * torch.rand(e, generator=g).double()
+            sums = [c[k * (e // count):(k + 1) * (e // count)].sort(descending=True).values[:2].sum()
+                    for k in range(count)]
+            gaps = [abs(float(a - b)) for k, a in enumerate(sums) for b in sums[k + 1:]]
+            if not gaps or min(gaps) >= 0.2:
+                break
+        w[f"l{i}.mlp.correction"] = c.float()
+        w[f"l{i}.mlp.router"] *= 0.08
 
 
 def make_movazen(folder, raw: dict, seed: int, dtype: str = "bfloat16", std: float = 0.15,
